@@ -7,6 +7,8 @@ from .girelix import ARCHITECTURE as GIRELIX_ARCHITECTURE
 from .girelix import GirelixConfig
 from .lfm2 import ARCHITECTURE as LFM2_ARCHITECTURE
 from .lfm2 import ConfigError, Lfm2Config
+from .penopel import ARCHITECTURE as PENOPEL_ARCHITECTURE
+from .penopel import PenopelConfig
 from .registry import (
     architecture_of,
     architectures,
@@ -17,8 +19,11 @@ from .registry import (
 from .specs import (
     AttentionSpec,
     DecayedLinearAttentionSpec,
+    DynamicTanhSpec,
     GatedDeltaSpec,
     GatedLinearAttentionSpec,
+    GatedMLPSpec,
+    LatentAttentionSpec,
     LayerSpec,
     ModelSpec,
     ParallelMixerSpec,
@@ -35,9 +40,10 @@ from .specs import (
 register_architecture(LFM2_ARCHITECTURE, Lfm2Config, model_type="lfm2")
 register_architecture(GIGUSUN_ARCHITECTURE, GigusunConfig)
 register_architecture(GIRELIX_ARCHITECTURE, GirelixConfig)
+register_architecture(PENOPEL_ARCHITECTURE, PenopelConfig)
 
 __all__ = [
-    "AttentionSpec", "ConfigError", "DecayedLinearAttentionSpec", "GirelixConfig", "ParallelMixerSpec", "RoutedExpertsSpec", "EngineConfig", "GatedDeltaSpec", "GatedLinearAttentionSpec", "GigusunConfig", "LayerSpec",
+    "AttentionSpec", "ConfigError", "DecayedLinearAttentionSpec", "DynamicTanhSpec", "GatedMLPSpec", "LatentAttentionSpec", "PenopelConfig", "GirelixConfig", "ParallelMixerSpec", "RoutedExpertsSpec", "EngineConfig", "GatedDeltaSpec", "GatedLinearAttentionSpec", "GigusunConfig", "LayerSpec",
     "Lfm2Config", "ModelSpec", "PartSpec", "PolyNormMLPSpec",
     "RMSNormSpec", "RopeSpec", "ScheduleEntry", "ShortConvSpec", "SwiGLUSpec", "architecture_of",
     "architectures", "config_from_dict", "load_config", "register_architecture",

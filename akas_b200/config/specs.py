@@ -37,6 +37,15 @@ class RMSNormSpec:
 
 
 @dataclass(frozen=True)
+class DynamicTanhSpec:
+    """y = tanh(alpha * x) * w + b: a norm that takes no mean and no variance. alpha is one learned number, w and b
+    are vectors of ``size``; in the checkpoint alpha and b stand beside the weight as ``<name>.alpha`` and ``<name>.b``."""
+
+    size: int
+    kind: str = "dynamic_tanh"
+
+
+@dataclass(frozen=True)
 class RopeSpec:
     """Rotary encoding of the first ``rotary_dim`` channels of each head: channel i turns with channel
     i + rotary / 2 (rotate-half), or, ``interleaved``, channel 2i with channel 2i + 1; the angle of pair i at
@@ -47,6 +56,10 @@ class RopeSpec:
     rotary_dim: Optional[int] = None  # None: the whole head
     kind: str = "rope"
     interleaved: bool = False  # only the general attention kernels take it
+    # Long waves slowed, as (factor, low, high, original): with wavelength l = 2 pi / f, a pair keeps its rate f where
+    # l < original / high, turns at f / factor where l > original / low, and in between at (1 - s) f / factor + s f with
+    # s = (original / l - low) / (high - low). None: every pair keeps its rate.
+    scaling: Optional[Tuple[float, float, float, float]] = None
 
     @property
     def rotary(self) -> int:
@@ -79,6 +92,10 @@ class AttentionSpec:
     # The values are the keys as projected (before QK-norm and the position encoding): there is no value matrix, and
     # the value heads have the keys' size.
     values_are_keys: bool = False
+    bias: bool = False  # q, k and v have biases (``<name>.b`` beside each matrix), added to the projections in float32
+    # False: the layer has no key and value projections; it reads the cache of another layer (the run order names
+    # whose), which holds that layer's keys after their rotation and its values, with queries and a mask of its own.
+    own_kv: bool = True
 
     @property
     def value_dim(self) -> int:
@@ -88,7 +105,37 @@ class AttentionSpec:
     def general(self) -> bool:
         """Whether the layer needs what only the general attention kernels compute."""
         return bool(self.v_head_dim not in (None, self.head_dim) or self.softcap or self.distance_bias or self.keep_first
-                    or self.sink or self.gate or self.values_are_keys or getattr(self.position, "interleaved", False))
+                    or self.sink or self.gate or self.values_are_keys or getattr(self.position, "interleaved", False)
+                    or self.bias or not self.own_kv)
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Attention whose queries, keys and values are projections of low-rank latents; only the key/value latent and one
+    rotated key part per token are kept.
+
+    c_q = RMSnorm(W_dq x) [q_rank]; q = W_uq c_q, per head [head_dim plain channels, rope_dim rotated]. W_dkv x has
+    kv_rank + rope_dim rows: the first kv_rank, RMS-normed, are the latent c; the last rope_dim, rotated (not normed),
+    are a key part that all heads share. Per head the plain key is W_uk c and the value W_uv c;
+    score = (q_plain . k_plain + q_rot . k_rot) * scale. ``window``: position i sees j with 0 <= i - j < window
+    (None: every earlier key). ``sink``: as for ``AttentionSpec``. ``gate="channel"``: the concatenated heads times
+    sigmoid(W_g x), element by element, before the output product."""
+
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    rope_dim: int
+    v_head_dim: int
+    q_rank: int
+    kv_rank: int
+    norm_eps: float
+    scale: float
+    position: Optional[Any] = None  # the rotation of the rope_dim part (a ``RopeSpec`` whose head is that part)
+    window: Optional[int] = None
+    sink: Any = False
+    gate: Optional[str] = None
+    kind: str = "latent_attention"
+    names: Mapping[str, str] = field(default_factory=dict)
 
 
 @dataclass(frozen=True)
@@ -109,6 +156,20 @@ class SwiGLUSpec:
     hidden_size: int
     intermediate_size: int
     kind: str = "swiglu"
+    names: Mapping[str, str] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class GatedMLPSpec:
+    """W_down (act(W_gate x + b_gate) * (W_up x + b_up)) + b_down with ``activation`` one of "gelu_tanh"
+    (0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))) and "silu"; ``bias``: the three projections have biases
+    (``<name>.b``), else none has."""
+
+    hidden_size: int
+    intermediate_size: int
+    activation: str = "gelu_tanh"
+    bias: bool = False
+    kind: str = "gated_mlp"
     names: Mapping[str, str] = field(default_factory=dict)
 
 

@@ -24,15 +24,18 @@ constexpr int kMaxGroup = 16;  // query heads of a key/value head that one block
 // given) the rotation of the first `rot` channels of each head by the token's angles, channel 2i with 2i + 1
 // (interleaved) or i with i + rot / 2; q to q_out [N, H * D], k and the untouched v into the pages at the token's
 // (page, offset). v may be the very rows of k: the values are then the keys as projected, before the rotation.
-template <typename T>
-__global__ void qk_norm_store_kernel(const T* __restrict__ q, long long ldq, const T* __restrict__ k, long long ldk,
-                                     const T* __restrict__ v, long long ldv, const float* __restrict__ qw,
+// Where biases are given (float32, one per channel of q, k, v), they are added first, in float32; q, k and v may then
+// be the float32 result of a product (TI) while the pages hold T, so product plus bias is rounded once.
+template <typename TI, typename T>
+__global__ void qk_norm_store_kernel(const TI* __restrict__ q, long long ldq, const TI* __restrict__ k, long long ldk,
+                                     const TI* __restrict__ v, long long ldv, const float* __restrict__ qw,
                                      const float* __restrict__ kw, float eps, T* __restrict__ q_out,
                                      T* __restrict__ k_pool, T* __restrict__ v_pool, const int* __restrict__ block_table,
                                      int max_blocks, const int* __restrict__ seq_of_token,
                                      const int* __restrict__ positions, int page_size, int H, int G, int D, int V, int write,
                                      const float* __restrict__ cos_t, const float* __restrict__ sin_t, int rot,
-                                     int interleaved) {
+                                     int interleaved, const float* __restrict__ qb, const float* __restrict__ kb,
+                                     const float* __restrict__ vb) {
   const int n = blockIdx.x;
   const int req = seq_of_token[n];
   if (req < 0) return;
@@ -43,36 +46,39 @@ __global__ void qk_norm_store_kernel(const T* __restrict__ q, long long ldq, con
   for (int head = warp; head < H + G; head += warps) {
     const bool is_q = head < H;
     if (!is_q && !write) continue;
-    const T* src = is_q ? q + (size_t)n * ldq + (size_t)head * D : k + (size_t)n * ldk + (size_t)(head - H) * D;
+    const TI* src = is_q ? q + (size_t)n * ldq + (size_t)head * D : k + (size_t)n * ldk + (size_t)(head - H) * D;
     const float* w = is_q ? qw : kw;
+    const float* bias = is_q ? (qb != nullptr ? qb + (size_t)head * D : nullptr) : (kb != nullptr ? kb + (size_t)(head - H) * D : nullptr);
+    auto at = [&](int d) { return bias != nullptr ? to_f32(src[d]) + bias[d] : to_f32(src[d]); };
     float inv = 1.f;
     if (w != nullptr) {
       float ss = 0.f;
-      for (int d = lane; d < D; d += 32) { const float x = to_f32(src[d]); ss = fmaf(x, x, ss); }
+      for (int d = lane; d < D; d += 32) { const float x = at(d); ss = fmaf(x, x, ss); }
       ss = warp_sum(ss);
       inv = 1.f / sqrtf(ss / (float)D + eps);
     }
     T* dst = is_q ? q_out + ((size_t)n * H + head) * D
                   : k_pool + (((size_t)page * G + (head - H)) * page_size + off) * D;
     if (cos_t == nullptr) {
-      for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>(w != nullptr ? to_f32(src[d]) * inv * w[d] : to_f32(src[d]));
+      for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>(w != nullptr ? at(d) * inv * w[d] : at(d));
       continue;
     }
     const int half = rot / 2;
     for (int i = lane; i < half; i += 32) {
       const int a = interleaved ? 2 * i : i, b = interleaved ? 2 * i + 1 : i + half;
-      float u = to_f32(src[a]), x = to_f32(src[b]);
+      float u = at(a), x = at(b);
       if (w != nullptr) { u *= inv * w[a]; x *= inv * w[b]; }
       const float c = cos_t[(size_t)n * half + i], sn = sin_t[(size_t)n * half + i];
       dst[a] = from_f32<T>(fmaf(u, c, -x * sn));
       dst[b] = from_f32<T>(fmaf(x, c, u * sn));
     }
-    for (int d = rot + lane; d < D; d += 32) dst[d] = from_f32<T>(w != nullptr ? to_f32(src[d]) * inv * w[d] : to_f32(src[d]));
+    for (int d = rot + lane; d < D; d += 32) dst[d] = from_f32<T>(w != nullptr ? at(d) * inv * w[d] : at(d));
   }
   if (write) {
     for (int i = threadIdx.x; i < G * V; i += blockDim.x) {
       const int g = i / V, j = i % V;
-      v_pool[(((size_t)page * G + g) * page_size + off) * V + j] = v[(size_t)n * ldv + i];
+      const float x = to_f32(v[(size_t)n * ldv + i]);
+      v_pool[(((size_t)page * G + g) * page_size + off) * V + j] = from_f32<T>(vb != nullptr ? x + vb[i] : x);
     }
   }
 }
@@ -117,7 +123,7 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
                          const int* __restrict__ positions, T* __restrict__ out, float scale, int window, int keep_first,
                          float cap, const float* __restrict__ r1, const float* __restrict__ r2, int sink,
                          const TG* __restrict__ gate, long long ldg, int page_size, int H, int G, int D, int V, int row_words,
-                         const float* __restrict__ sinks, float out_scale, long long ldo) {
+                         const float* __restrict__ sinks, float out_scale, long long ldo, long long vpitch) {
   extern __shared__ __align__(16) float smem[];
   const int n = blockIdx.x, g = blockIdx.y;
   const int req = seq_of_token[n];
@@ -220,7 +226,7 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
           for (int a = 0; a < kMaxGroup; ++a) add[a] = 0.f;
 #pragma unroll 8
           for (int t = begin; t < count; ++t) {  // (the rows' places were found with the scores: these loads do not wait on one another)
-            const float vv = to_f32(v_pool[(size_t)rowbase[t] * V + c]);
+            const float vv = to_f32(v_pool[(size_t)rowbase[t] * vpitch + c]);
 #pragma unroll
             for (int a = 0; a < kMaxGroup; ++a)
               if (a < heads) add[a] = fmaf(pw[a * kTile + t], vv, add[a]);
@@ -256,16 +262,22 @@ AKAS_API int akas_qk_norm_store(const void* q, long long ldq, const void* k, lon
                                 const float* qw, const float* kw, float eps, void* q_out, void* k_pool, void* v_pool,
                                 const int* block_table, int max_blocks, const int* seq_of_token, const int* positions,
                                 int page_size, int N, int H, int G, int D, int V, int write, int dtype, const float* cos_t,
-                                const float* sin_t, int rot, int interleaved, cudaStream_t stream) {
+                                const float* sin_t, int rot, int interleaved, int in_dtype, const float* qb, const float* kb,
+                                const float* vb, cudaStream_t stream) {
   if (N <= 0) return 0;
   if (cos_t != nullptr && (rot <= 0 || rot % 2 || rot > D)) return (int)cudaErrorInvalidValue;
+  if (dtype == AKAS_F32 && in_dtype != AKAS_F32) return (int)cudaErrorInvalidValue;
   if (dtype == AKAS_F32)
-    return launch_ordinary(qk_norm_store_kernel<float>, dim3(N), dim3(128), 0, stream, (const float*)q, ldq, (const float*)k, ldk,
+    return launch_ordinary(qk_norm_store_kernel<float, float>, dim3(N), dim3(128), 0, stream, (const float*)q, ldq, (const float*)k, ldk,
                           (const float*)v, ldv, qw, kw, eps, (float*)q_out, (float*)k_pool, (float*)v_pool, block_table,
-                          max_blocks, seq_of_token, positions, page_size, H, G, D, V, write, cos_t, sin_t, rot, interleaved);
-  return launch_ordinary(qk_norm_store_kernel<bf16>, dim3(N), dim3(128), 0, stream, (const bf16*)q, ldq, (const bf16*)k, ldk,
+                          max_blocks, seq_of_token, positions, page_size, H, G, D, V, write, cos_t, sin_t, rot, interleaved, qb, kb, vb);
+  if (in_dtype == AKAS_F32)
+    return launch_ordinary(qk_norm_store_kernel<float, bf16>, dim3(N), dim3(128), 0, stream, (const float*)q, ldq, (const float*)k, ldk,
+                          (const float*)v, ldv, qw, kw, eps, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool, block_table, max_blocks,
+                          seq_of_token, positions, page_size, H, G, D, V, write, cos_t, sin_t, rot, interleaved, qb, kb, vb);
+  return launch_ordinary(qk_norm_store_kernel<bf16, bf16>, dim3(N), dim3(128), 0, stream, (const bf16*)q, ldq, (const bf16*)k, ldk,
                         (const bf16*)v, ldv, qw, kw, eps, (bf16*)q_out, (bf16*)k_pool, (bf16*)v_pool, block_table, max_blocks,
-                        seq_of_token, positions, page_size, H, G, D, V, write, cos_t, sin_t, rot, interleaved);
+                        seq_of_token, positions, page_size, H, G, D, V, write, cos_t, sin_t, rot, interleaved, qb, kb, vb);
 }
 
 template <typename T, typename TG>
@@ -273,7 +285,7 @@ static int launch_general(const void* q, const void* k_pool, const void* v_pool,
                           const int* seq_of_token, const int* positions, void* out, float scale, int window, int keep_first,
                           float cap, const float* r1, const float* r2, int sink, const void* gate, long long ldg,
                           int page_size, int N, int H, int G, int D, int V, const float* sinks, float out_scale,
-                          long long ldo, cudaStream_t stream) {
+                          long long ldo, long long vpitch, cudaStream_t stream) {
   const int Vp = (V + kTile - 1) / kTile * kTile;
   const int row_words = (kMaxGroup * D + kMaxGroup * kTile + kMaxGroup * 4 + kMaxGroup * 2 + kMaxGroup * Vp + 1) / 2 * 2;
   const size_t smem = sizeof(float) * (size_t)row_words + sizeof(long long) * kTile;
@@ -288,19 +300,20 @@ static int launch_general(const void* q, const void* k_pool, const void* v_pool,
   }
   return launch_ordinary(attention_general_kernel<T, TG>, dim3(N, G), dim3(kTile), smem, stream, (const T*)q, (const T*)k_pool,
                         (const T*)v_pool, block_table, max_blocks, seq_of_token, positions, (T*)out, scale, window, keep_first,
-                        cap, r1, r2, sink, (const TG*)gate, ldg, page_size, H, G, D, V, row_words, sinks, out_scale, ldo);
+                        cap, r1, r2, sink, (const TG*)gate, ldg, page_size, H, G, D, V, row_words, sinks, out_scale, ldo, vpitch);
 }
 
 AKAS_API int akas_attention_general(const void* q, const void* k_pool, const void* v_pool, const int* block_table,
                                     int max_blocks, const int* seq_of_token, const int* positions, void* out, float scale,
                                     int window, int keep_first, float cap, const float* r1, const float* r2, int sink,
                                     const void* gate, long long ldg, int page_size, int N, int H, int G, int D, int V,
-                                    int dtype, const float* sinks, float out_scale, long long ldo, cudaStream_t stream) {
+                                    int dtype, const float* sinks, float out_scale, long long ldo, long long vpitch,
+                                    cudaStream_t stream) {
   if (N <= 0) return 0;
-  if (G <= 0 || H % G) return (int)cudaErrorInvalidValue;
+  if (G <= 0 || H % G || vpitch < V) return (int)cudaErrorInvalidValue;
   if (dtype == AKAS_F32)
     return launch_general<float, float>(q, k_pool, v_pool, block_table, max_blocks, seq_of_token, positions, out, scale, window,
-                                        keep_first, cap, r1, r2, sink, gate, ldg, page_size, N, H, G, D, V, sinks, out_scale, ldo, stream);
+                                        keep_first, cap, r1, r2, sink, gate, ldg, page_size, N, H, G, D, V, sinks, out_scale, ldo, vpitch, stream);
   return launch_general<bf16, bf16>(q, k_pool, v_pool, block_table, max_blocks, seq_of_token, positions, out, scale, window,
-                                    keep_first, cap, r1, r2, sink, gate, ldg, page_size, N, H, G, D, V, sinks, out_scale, ldo, stream);
+                                    keep_first, cap, r1, r2, sink, gate, ldg, page_size, N, H, G, D, V, sinks, out_scale, ldo, vpitch, stream);
 }

@@ -52,6 +52,7 @@ struct Options {
   const float* sinks;  // a learned sink logit per head, or null
   float out_scale;
   long long ldo;       // elements between the output rows of two tokens
+  long long vpitch;    // elements between two value rows in the pages (V, or more where a row holds more than the value)
 };
 
 constexpr int kTableBefore = 128, kTableAfter = 192;  // entries of the penalty table on either side of the window's distances
@@ -135,7 +136,7 @@ general_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
         cp_async16(ks_ + row * KSTRIDE + col, k_pool + base * D + min(col, D - 8), page >= 0 && col < D ? 16 : 0);
       } else {
         const int col = (ch - KCH) * 8;
-        cp_async16(vs_ + row * VSTRIDE + col, v_pool + base * V + min(col, V - 8), page >= 0 && col < V ? 16 : 0);
+        cp_async16(vs_ + row * VSTRIDE + col, v_pool + base * opt.vpitch + min(col, V - 8), page >= 0 && col < V ? 16 : 0);
       }
     }
     cp_async_commit();
@@ -400,15 +401,15 @@ AKAS_API int akas_attention_general_tc(const void* q, const void* k_pool, const 
                                        int window, int keep_first, float cap, const float* r1, const float* r2, int sink,
                                        const void* gate, long long ldg, int page_size, int tiles, int H, int KH, int D, int V,
                                        int R, int packed, const float* sinks, float out_scale, long long ldo, float* partial,
-                                       int splits, cudaStream_t stream) {
+                                       int splits, long long vpitch, cudaStream_t stream) {
   if (!akas_attention_general_tc_takes(D, V)) return 3999;
-  if (ldo % 2) return 3999;
+  if (ldo % 2 || vpitch % 8 || vpitch < V) return 3999;
   // parts: packed launches only; partial holds (first token of the launch + R) * H * splits * (V + 2) floats
   if (splits < 1 || splits > 64 || (splits > 1 && (!packed || partial == nullptr))) return (int)cudaErrorInvalidValue;
   if (packed && (KH <= 0 || H / KH > BQ || tiles != R)) return 3999;
   if (KH <= 0 || H % KH || tiles > 65535 || R <= 0) return (int)cudaErrorInvalidValue;
   if (tiles <= 0) return 0;
-  const Options opt = {scale, cap, r1, r2, window, keep_first, sink, (const bf16*)gate, ldg, sinks, out_scale, ldo};
+  const Options opt = {scale, cap, r1, r2, window, keep_first, sink, (const bf16*)gate, ldg, sinks, out_scale, ldo, vpitch};
   const int dk = (D + 31) / 32, dv = (V + 31) / 32;
 #define AKAS_TC(A, B)                                                                                                   \
   if (dk == A && dv == B)                                                                                               \

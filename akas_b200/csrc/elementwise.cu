@@ -375,3 +375,78 @@ AKAS_API int akas_polynorm(const void* z, const float* coeffs, float eps, void* 
   else AKAS_POLY(bf16, bf16)
 #undef AKAS_POLY
 }
+
+// Dynamic Tanh, a norm without statistics: y[m, c] = tanh(alpha * x[row(m), c]) * w[c] + b[c], float32 throughout,
+// rounded once on the way out. alpha is one number on the device. rows: optional gather of the rows to norm.
+template <typename TO>
+__global__ void dynamic_tanh_kernel(const float* __restrict__ x, const float* __restrict__ alpha, const float* __restrict__ w,
+                                    const float* __restrict__ b, TO* __restrict__ y, const int* __restrict__ rows, int C,
+                                    size_t total) {
+  const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= total) return;
+  const float a = alpha[0];
+  if (C % 4 == 0) {  // four channels of one row, 16 bytes in
+    const size_t m = i / C;
+    const int c = (int)(i % C);
+    const size_t src = (rows != nullptr ? (size_t)rows[m] : m) * C + c;
+    const float4 v = *reinterpret_cast<const float4*>(x + src);
+    const float4 wv = *reinterpret_cast<const float4*>(w + c), bv = *reinterpret_cast<const float4*>(b + c);
+    y[i] = from_f32<TO>(fmaf(tanhf(a * v.x), wv.x, bv.x));
+    y[i + 1] = from_f32<TO>(fmaf(tanhf(a * v.y), wv.y, bv.y));
+    y[i + 2] = from_f32<TO>(fmaf(tanhf(a * v.z), wv.z, bv.z));
+    y[i + 3] = from_f32<TO>(fmaf(tanhf(a * v.w), wv.w, bv.w));
+    return;
+  }
+  for (size_t j = i; j < total && j < i + 4; ++j) {
+    const size_t m = j / C;
+    const int c = (int)(j % C);
+    const size_t src = (rows != nullptr ? (size_t)rows[m] : m) * C + c;
+    y[j] = from_f32<TO>(fmaf(tanhf(a * x[src]), w[c], b[c]));
+  }
+}
+
+AKAS_API int akas_dynamic_tanh(const float* x, const float* alpha, const float* w, const float* b, void* y, const int* rows,
+                               int M, int C, int out_dtype, cudaStream_t stream) {
+  const size_t total = (size_t)M * C;
+  if (total == 0) return 0;
+  const unsigned blocks = (unsigned)((total + 1023) / 1024);
+  if (out_dtype == AKAS_F32) dynamic_tanh_kernel<float><<<blocks, 256, 0, stream>>>(x, alpha, w, b, (float*)y, rows, C, total);
+  else dynamic_tanh_kernel<bf16><<<blocks, 256, 0, stream>>>(x, alpha, w, b, (bf16*)y, rows, C, total);
+  return launch_status();
+}
+
+// The middle of a gated feed-forward whose first product left float32: out[n, f] = act(g + b_g) * (u + b_u) with
+// g = gu[n, f], u = gu[n, F + f] (rows of pitch ld), biases optional, act the tanh form of gelu (0) or silu (1);
+// float32 until the one rounding. The same launch adds the last product's bias to the residual stream
+// (res[n, c] += res_bias[c], float32 [N, C]) where one is given, so that product can accumulate into it.
+__device__ __forceinline__ float gelu_tanh_f32(float z) {
+  return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+template <typename TO>
+__global__ void gated_activation_kernel(const float* __restrict__ gu, long long ld, const float* __restrict__ bias,
+                                        TO* __restrict__ out, int F, int act, float* __restrict__ res,
+                                        const float* __restrict__ res_bias, int C) {
+  const int n = blockIdx.x;
+  const float* row = gu + (size_t)n * ld;
+  for (int f = threadIdx.x; f < F; f += blockDim.x) {
+    float g = row[f], u = row[F + f];
+    if (bias != nullptr) { g += bias[f]; u += bias[F + f]; }
+    const float a = act == 0 ? gelu_tanh_f32(g) : g / (1.f + expf(-g));
+    out[(size_t)n * F + f] = from_f32<TO>(a * u);
+  }
+  if (res != nullptr)
+    for (int c = threadIdx.x; c < C; c += blockDim.x) res[(size_t)n * C + c] += res_bias[c];
+}
+
+AKAS_API int akas_gated_activation(const float* gu, long long ld, const float* bias, void* out, int N, int F, int act,
+                                   int out_dtype, float* res, const float* res_bias, int C, cudaStream_t stream) {
+  if (N <= 0 || F <= 0) return 0;
+  if (act != 0 && act != 1) return (int)cudaErrorInvalidValue;
+  const int threads = F >= 1024 ? 256 : 128;
+  if (out_dtype == AKAS_F32)
+    gated_activation_kernel<float><<<N, threads, 0, stream>>>(gu, ld, bias, (float*)out, F, act, res, res_bias, C);
+  else
+    gated_activation_kernel<bf16><<<N, threads, 0, stream>>>(gu, ld, bias, (bf16*)out, F, act, res, res_bias, C);
+  return launch_status();
+}

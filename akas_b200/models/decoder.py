@@ -18,7 +18,7 @@ from typing import Callable, Dict, List, Optional
 import torch
 
 from ..config.specs import ModelSpec
-from ..parts.base import Param, Runtime, build_part, project
+from ..parts.base import Param, Runtime, build_part, load_norm, norm_params, project
 from ..parts.block import Block
 
 
@@ -52,15 +52,13 @@ class Decoder:
     def params(self) -> Dict[str, Param]:
         s = self.spec
         out = {s.embedding_name: Param((s.vocab_size, s.hidden_size))}
-        (norm_param,) = self.final_norm.params().values()
-        out[s.final_norm_name] = norm_param
+        out.update(norm_params(self.final_norm, s.final_norm_name))
         if s.head_name is not None:
             out[s.head_name] = Param((s.vocab_size, s.hidden_size), optional=s.head_optional)
         if s.position_table_name is not None:
             out[s.position_table_name] = Param((s.max_context, s.hidden_size))
         if self.embedding_norm is not None:
-            (norm_param,) = self.embedding_norm.params().values()
-            out[s.embedding_norm_name] = norm_param
+            out.update(norm_params(self.embedding_norm, s.embedding_norm_name))
         for block in self.blocks:
             out.update(block.params())
         return out
@@ -68,11 +66,11 @@ class Decoder:
     def load(self, get: Callable[[str], torch.Tensor], has: Callable[[str], bool] = lambda name: True) -> None:
         s = self.spec
         self.embedding = get(s.embedding_name)
-        self.final_norm.load(lambda _name: get(s.final_norm_name))
+        load_norm(self.final_norm, s.final_norm_name, get)
         if s.position_table_name is not None:
             self.positions = get(s.position_table_name)
         if self.embedding_norm is not None:
-            self.embedding_norm.load(lambda _name: get(s.embedding_norm_name))
+            load_norm(self.embedding_norm, s.embedding_norm_name, get)
         self.head = get(s.head_name) if s.head_name is not None and has(s.head_name) else self.embedding
         for block in self.blocks:
             block.load(get)

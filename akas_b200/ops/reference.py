@@ -398,15 +398,29 @@ def gated_rmsnorm(o, weight, eps, gate, heads, vdim, out_dtype, gate_activation=
 
 
 def qk_norm_store(q, k, v, heads, kv_heads, dim, vdim, q_weight, k_weight, eps, k_pool, v_pool, block_table,
-                  seq_of_token, positions, page_size, write=True, cos=None, sin=None, interleaved=False):
-    """Per-head RMSNorm (plain weight; None: no norm) of q [N, heads * dim] and k [N, kv_heads * dim], then, where
+                  seq_of_token, positions, page_size, write=True, cos=None, sin=None, interleaved=False,
+                  q_bias=None, k_bias=None, v_bias=None):
+    """First, where biases (float32 [heads * dim], [kv_heads * dim], [kv_heads * vdim]) are given, q, k and v plus
+    their biases (q, k and v may then be float32 results of a product, rounded here for the first time). Then
+    per-head RMSNorm (plain weight; None: no norm) of q [N, heads * dim] and k [N, kv_heads * dim], then, where
     ``cos`` and ``sin`` (float32 [N, rot / 2]) are given, the rotation of the first ``rot`` channels of every head of
     q and k: channel 2i with 2i + 1 (``interleaved``) or i with i + rot / 2. k and the untouched v [N, kv_heads * vdim]
     go into the pages (k pages [.., kv_heads, page, dim], v pages [.., kv_heads, page, vdim]); returns q, contiguous,
     in the pools' dtype."""
     n = q.shape[0]
-    qf = q.to(torch.float32).reshape(n, heads, dim)
-    kf = k.to(torch.float32).reshape(n, kv_heads, dim)
+    qf = q.to(torch.float32)
+    if q_bias is not None:
+        qf = qf + q_bias
+    qf = qf.reshape(n, heads, dim)
+    if write:
+        kf, vf = k.to(torch.float32), v.to(torch.float32)
+        if k_bias is not None:
+            kf = kf + k_bias
+        if v_bias is not None:
+            vf = vf + v_bias
+        kf = kf.reshape(n, kv_heads, dim)
+    else:
+        kf = torch.zeros((n, kv_heads, dim), dtype=torch.float32, device=q.device)  # nothing of k and v is read
     if q_weight is not None:
         qf = rmsnorm(qf, q_weight, eps, False, torch.float32)
         kf = rmsnorm(kf, k_weight, eps, False, torch.float32)
@@ -429,19 +443,22 @@ def qk_norm_store(q, k, v, heads, kv_heads, dim, vdim, q_weight, k_weight, eps, 
     if write:
         live, page, off = _page_addresses(block_table, seq_of_token, positions, page_size)
         k_pool[page[live], :, off[live]] = kf[live].to(k_pool.dtype)
-        v_pool[page[live], :, off[live]] = v.reshape(n, kv_heads, vdim)[live].to(v_pool.dtype)
+        v_pool[page[live], :, off[live]] = vf.reshape(n, kv_heads, vdim)[live].to(v_pool.dtype)
     return qf.reshape(n, heads * dim).to(k_pool.dtype).contiguous()
 
 
 def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, scale, window, keep_first, softcap,
-                      r1, r2, sink, gate, page_size, ctx=None, sinks=None, out=None, out_scale=1.0):
-    """Attention of every token over the keys of its request that it sees: j <= i and (no window, or i - j < window,
+                      r1, r2, sink, gate, page_size, ctx=None, sinks=None, out=None, out_scale=1.0, values_in_keys=0):
+    """``values_in_keys`` = V > 0: a key's row holds its value too, as its first V channels (``v_pool`` is not read).
+    Attention of every token over the keys of its request that it sees: j <= i and (no window, or i - j < window,
     or j < keep_first). score = q . k * scale; with softcap, cap * tanh(score / cap); with r1 and r2 (float32
     [heads]), minus r1_h * ln(1 + r2_h * (i - j)); softmax over the keys, with ``sink`` one more term exp(0) in the
     denominator, or with ``sinks`` (float32 [heads]) the term exp(sinks_h); the head's output times
     sigmoid(gate[n, h]) where ``gate`` [N, heads] is given, times ``out_scale``.
     q [N, heads * dim] -> [N, heads * vdim] in q's dtype, written into ``out`` (rows may be parts of wider rows) where given."""
     n = q.shape[0]
+    if values_in_keys:
+        v_pool = k_pool[..., :values_in_keys]
     kh, d, vd = k_pool.shape[1], k_pool.shape[3], v_pool.shape[3]
     heads = q.shape[1] // d
     group = heads // kh
@@ -484,6 +501,90 @@ def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, s
         given.copy_(result.to(given.dtype))
         return given
     return result.to(q.dtype)
+
+
+# --------------------------------------------------------------------------- latent attention, norms without sums
+
+
+def dynamic_tanh(x, alpha, weight, shift, out_dtype, rows=None):
+    """tanh(alpha * x) * weight + shift per element of float32 x [N, C] (alpha a float32 tensor of one number, weight
+    and shift float32 [C]); ``rows``: int32 indices of the rows to norm and return."""
+    if rows is not None:
+        x = x[rows.long()]
+    y = torch.tanh(alpha.to(torch.float32) * x.to(torch.float32)) * weight + shift
+    return y.to(out_dtype)
+
+
+def _activation(z, kind):
+    if kind == "gelu_tanh":
+        return 0.5 * z * (1.0 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z * z * z)))
+    if kind == "silu":
+        return z * torch.sigmoid(z)
+    raise ValueError(f"unknown activation {kind!r}")
+
+
+def gated_activation(gate_up, width, bias, activation, out_dtype):
+    """act(g + b_g) * (u + b_u) for float32 gate_up [N, >= 2 width] whose first ``width`` columns are g and whose next
+    are u; bias float32 [2 width] (b_g then b_u) or None -> [N, width] in ``out_dtype``, rounded once."""
+    g, u = gate_up[:, :width].to(torch.float32), gate_up[:, width : 2 * width].to(torch.float32)
+    if bias is not None:
+        g, u = g + bias[:width], u + bias[width:]
+    return (_activation(g, activation) * u).to(out_dtype)
+
+
+def latent_norm_store(proj, q_rank, kv_rank, rot, q_weight, kv_weight, eps, cos, sin, interleaved, pool, block_table,
+                      seq_of_token, positions, page_size, write=True):
+    """From a row of proj [N, >= q_rank + kv_rank + rot] (float32): its first q_rank columns over their root mean
+    square (eps under the root) times q_weight -> returned [N, q_rank] in the pool's dtype. The next kv_rank columns
+    over THEIR root mean square times kv_weight, then the last rot columns rotated as a whole (cos, sin float32
+    [N, rot / 2]; pairs (2i, 2i + 1) when ``interleaved``, else (i, i + rot / 2); no tables: as they are) -> the
+    token's row [kv_rank + rot] of ``pool`` [pages, 1, page, kv_rank + rot]."""
+    n = proj.shape[0]
+    pf = proj.to(torch.float32)
+    out = rmsnorm(pf[:, :q_rank], q_weight, eps, False, pool.dtype)
+    if write:
+        c = rmsnorm(pf[:, q_rank : q_rank + kv_rank], kv_weight, eps, False, torch.float32)
+        tail = pf[:, q_rank + kv_rank : q_rank + kv_rank + rot]
+        if cos is not None and rot:
+            tail = _turn(tail.reshape(n, 1, rot), cos, sin, interleaved).reshape(n, rot)
+        live, page, off = _page_addresses(block_table, seq_of_token, positions, page_size)
+        pool[page[live], 0, off[live]] = torch.cat((c, tail), dim=1)[live].to(pool.dtype)
+    return out.contiguous()
+
+
+def _turn(x, cos, sin, interleaved):
+    """The first 2 * cos.shape[1] channels of every head of float32 x [N, heads, D] rotated by the token's angles."""
+    half = cos.shape[1]
+    c, sn = cos[:, None, :].to(torch.float32), sin[:, None, :].to(torch.float32)
+    x = x.clone()
+    a = x[..., 0 : 2 * half : 2] if interleaved else x[..., :half]
+    b = x[..., 1 : 2 * half : 2] if interleaved else x[..., half : 2 * half]
+    ra, rb = a * c - b * sn, b * c + a * sn
+    if interleaved:
+        x[..., 0 : 2 * half : 2], x[..., 1 : 2 * half : 2] = ra, rb
+    else:
+        x[..., :half], x[..., half : 2 * half] = ra, rb
+    return x
+
+
+def head_linear(x, w, heads, gate=None, cos=None, sin=None, interleaved=False):
+    """A product per head: for w [heads, O, K] and x [N, heads * (K + T)] (head h's K channels, then T more),
+    out[n, h, :O] = w[h] x[n, h, :K], float32 accumulation, and out[n, h, O:] = the head's T further channels, rotated
+    as a whole where ``cos`` and ``sin`` (float32 [N, T / 2]) are given. ``gate`` [N, heads * O] (any float dtype, rows
+    may be parts of wider rows): the products times sigmoid(gate). -> [N, heads * (O + T)] in x's dtype."""
+    n = x.shape[0]
+    h, o, k = w.shape
+    t = x.shape[1] // heads - k
+    xf = x.to(torch.float32).reshape(n, heads, k + t)
+    y = torch.einsum("nhk,hok->nho", xf[:, :, :k], w.to(torch.float32))
+    if gate is not None:
+        y = y * torch.sigmoid(gate.to(torch.float32).reshape(n, heads, o))
+    if t:
+        tail = xf[:, :, k:]
+        if cos is not None:
+            tail = _turn(tail, cos, sin, interleaved)
+        y = torch.cat((y, tail), dim=2)
+    return y.reshape(n, heads * (o + t)).to(x.dtype)
 
 
 # --------------------------------------------------------------------------- routed experts, parallel blocks

@@ -5,6 +5,7 @@ from .base import (
     Mixer,
     Normed,
     PagedKVSpec,
+    PagedLatentSpec,
     PagedSpec,
     Param,
     Part,
@@ -20,8 +21,10 @@ from .base import (
 )
 from .attention import Attention
 from .block import ARRANGEMENTS, Block
+from .gated_mlp import GatedMLP
+from .latent import LatentAttention
 from .moe import RoutedExperts
-from .norm import RMSNorm
+from .norm import DynamicTanh, RMSNorm
 from .parallel import ParallelMixer
 from .polynorm import PolyNormMLP
 from .recurrent import DecayedLinearAttention, GatedDelta, GatedLinearAttention
@@ -30,7 +33,7 @@ from .shortconv import ShortConv
 from .swiglu import SwiGLU
 
 __all__ = [
-    "ARRANGEMENTS", "Attention", "Block", "DecayedLinearAttention", "ParallelMixer", "RoutedExperts", "FeedForward", "GatedDelta", "GatedLinearAttention", "Mixer", "PolyNormMLP", "Normed", "PagedKVSpec", "PagedSpec", "Param", "Part", "RMSNorm",
+    "ARRANGEMENTS", "Attention", "Block", "DynamicTanh", "GatedMLP", "LatentAttention", "PagedLatentSpec", "DecayedLinearAttention", "ParallelMixer", "RoutedExperts", "FeedForward", "GatedDelta", "GatedLinearAttention", "Mixer", "PolyNormMLP", "Normed", "PagedKVSpec", "PagedSpec", "Param", "Part", "RMSNorm",
     "Rope", "Runtime", "ShortConv", "StateSpec", "SwiGLU", "build_part", "project", "project_swiglu", "register_ffn", "register_mixer",
     "register_norm", "register_position",
 ]

@@ -11,7 +11,8 @@ and to itself; the output product, added to the residual.
 A layer whose spec asks for more than that (value heads of another size than the keys', a capped score, a
 logarithmic distance penalty, first tokens kept behind the window, a sink in the softmax's denominator (exp(0) or a
 learned logit per head), a gate per head on the output, values that are the keys as projected, rotary pairs of
-neighbouring channels) runs the same steps on the general kernels: one product for q, k, v and the gate's
+neighbouring channels, biases on q, k and v, no keys and values of its own but another layer's cache) runs the same
+steps on the general kernels: one product for q, k, v and the gate's
 logits, QK-norm, rotation and page write (``ops.qk_norm_store``), attention with the options as arguments
 (``ops.attention_general``), the output product. ``core`` is that sequence without the two products, for a mixer
 that stacks this one's matrices with its neighbours' (``parts/parallel.py``).
@@ -51,6 +52,10 @@ class Attention(Mixer):
             raise ValueError(f"unknown output gate {s.gate!r}; known: 'head'")
         if self.general and s.keep_first and not s.window:
             raise ValueError("keep_first needs a window")
+        self.own_kv = bool(getattr(s, "own_kv", True))
+        self.biased = bool(getattr(s, "bias", False))
+        if not self.own_kv and getattr(s, "values_are_keys", False):
+            raise ValueError("a layer without keys of its own has no values that are its keys")
         self.q_norm = build_part("norm", s.qk_norm, runtime)
         self.k_norm = build_part("norm", s.qk_norm, runtime)
         self.position = build_part("position", s.position, runtime)
@@ -59,7 +64,7 @@ class Attention(Mixer):
             raise ValueError("the general attention kernels take a position encoding by rotary tables only")
         self.w_qkv = None
         self.w_out = None
-        self.r1 = self.r2 = self.sinks = None
+        self.r1 = self.r2 = self.sinks = self.bias = None
 
     def _n(self, local):
         return renamed(self.spec, local)
@@ -75,6 +80,13 @@ class Attention(Mixer):
         }
         if self.general and s.values_are_keys:
             del p[self._n("v_proj.weight")]
+        if not self.own_kv:
+            p.pop(self._n("k_proj.weight"))
+            p.pop(self._n("v_proj.weight"), None)
+        if self.biased:
+            for local in ("q_proj.weight", "k_proj.weight", "v_proj.weight"):
+                if self._n(local) in p:
+                    p[self._n(local) + ".b"] = Param((p[self._n(local)].shape[0],), role="vector")
         if self.general and s.sink == "learned":
             p[self._n("sink")] = Param((s.num_heads,), role="vector")
         if self.general and s.gate == "head":
@@ -90,12 +102,17 @@ class Attention(Mixer):
 
     def load(self, get):
         if self.general:
-            parts = [get(self._n("q_proj.weight")), get(self._n("k_proj.weight"))]
-            if not self.spec.values_are_keys:
-                parts.append(get(self._n("v_proj.weight")))
+            names = [self._n("q_proj.weight")]
+            if self.own_kv:
+                names.append(self._n("k_proj.weight"))
+                if not self.spec.values_are_keys:
+                    names.append(self._n("v_proj.weight"))
+            parts = [get(name) for name in names]
             if self.spec.gate == "head":
                 parts.append(get(self._n("gate.weight")))
             self.w_qkv = stack_rows(parts)
+            if self.biased:
+                self.bias = torch.cat([get(name + ".b") for name in names]).contiguous()
             if self.spec.sink == "learned":
                 self.sinks = get(self._n("sink"))
             if self.spec.distance_bias:
@@ -111,6 +128,8 @@ class Attention(Mixer):
 
     def cache(self):
         s = self.spec
+        if not self.own_kv:
+            raise ValueError("this attention layer keeps no keys and values: the run order must give it another layer's cache")
         if self.general:
             return PagedKVSpec(s.num_kv_heads, s.head_dim, s.window, keep_first=s.keep_first if s.window else 0,
                                v_head_dim=s.value_dim)
@@ -128,10 +147,14 @@ class Attention(Mixer):
         if not self.general:
             raise ValueError("core() is the general layers' sequence")
         s, ops = self.spec, self.rt.ops
-        nq, nk = s.num_heads * s.head_dim, s.num_kv_heads * s.head_dim
-        nv = 0 if s.values_are_keys else s.num_kv_heads * s.value_dim
-        q, k = proj[:, :nq], proj[:, nq : nq + nk]
-        v = k if s.values_are_keys else proj[:, nq + nk : nq + nk + nv]
+        if not self.own_kv and write:
+            raise ValueError("a layer without keys and values of its own writes no cache")
+        nq = s.num_heads * s.head_dim
+        nk = s.num_kv_heads * s.head_dim if self.own_kv else 0
+        nv = 0 if s.values_are_keys or not self.own_kv else s.num_kv_heads * s.value_dim
+        q = proj[:, :nq]
+        k = proj[:, nq : nq + nk] if self.own_kv else q  # (with nothing to write, k and v are not read)
+        v = k if s.values_are_keys or not self.own_kv else proj[:, nq + nk : nq + nk + nv]
         gate = proj[:, nq + nk + nv : nq + nk + nv + s.num_heads] if s.gate == "head" else None
         norm = self.q_norm.spec if self.q_norm is not None else None
         if norm is not None and norm.zero_centered:
@@ -141,6 +164,9 @@ class Attention(Mixer):
         if self.position is not None:
             cos, sin = self.position.tables(ctx)
             rotary = dict(cos=cos, sin=sin, interleaved=self.position.interleaved)
+        if self.bias is not None:
+            rotary.update(q_bias=self.bias[:nq], k_bias=self.bias[nq : nq + nk] if nk else None,
+                          v_bias=self.bias[nq + nk : nq + nk + nv] if nv else None)
         qn = ops.qk_norm_store(
             q, k, v, s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim,
             self.q_norm.weight if norm else None, self.k_norm.weight if norm else None, norm.eps if norm else 0.0,
@@ -159,7 +185,9 @@ class Attention(Mixer):
         )
 
     def _forward_general(self, x, ctx, cache, residual, write):
-        out = self.core(project(self.rt, x, self.w_qkv), ctx, cache, write)
+        # with biases the product leaves float32, so that product plus bias is rounded once (by the kernel that adds it)
+        proj = project(self.rt, x, self.w_qkv, out_dtype=torch.float32 if self.bias is not None else None)
+        out = self.core(proj, ctx, cache, write)
         return project(self.rt, out, self.w_out, residual=residual)
 
     def forward(self, x, ctx, cache=None, residual=None, write=True):

@@ -101,6 +101,21 @@ class PagedKVSpec(PagedSpec):
 
 
 @dataclass(frozen=True)
+class PagedLatentSpec(PagedSpec):
+    """One row of ``width`` numbers per position (or per position of the last ``window``) that serves as key and,
+    by its first channels, as value for every head: pages ``[1, page, width]`` in one pool, ``kv``."""
+
+    width: int = 16
+    window: Optional[int] = None
+    page_size: Optional[int] = None
+    dtype: Optional[torch.dtype] = None
+    keep_first: int = 0
+
+    def pools(self, page_size: int) -> Dict[str, Tuple[int, ...]]:
+        return {"kv": (1, page_size, self.width)}
+
+
+@dataclass(frozen=True)
 class StateSpec:
     """Per-request state of fixed size: one row of ``shape`` per request slot, zero at admission."""
 
@@ -249,6 +264,23 @@ def build_part(family: str, spec, runtime: Runtime):
     if kind not in table:
         raise KeyError(f"no {family} registered for kind {kind!r}; registered: {sorted(table)}")
     return table[kind](spec, runtime)
+
+
+def norm_params(norm, name: str) -> Dict[str, Param]:
+    """Checkpoint name -> Param for a norm whose weight a layer names whole (``name``). A norm with more tensors than
+    its weight lists the weight first and the others under local names that start with a dot; they stand beside the
+    weight as ``name + local``."""
+    items = list(norm.params().items())
+    out = {name: items[0][1]}
+    for local, param in items[1:]:
+        out[name + local] = param
+    return out
+
+
+def load_norm(norm, name: str, get: Callable[[str], torch.Tensor]) -> None:
+    """Hands a norm its tensors from the names that ``norm_params`` gave them."""
+    main = next(iter(norm.params()))
+    norm.load(lambda local: get(name if local == main else name + local))
 
 
 def stack_rows(matrices, multiple: int = 16) -> torch.Tensor:

@@ -11,7 +11,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import Param, Runtime, build_part
+from .base import Param, Runtime, build_part, load_norm, norm_params
 
 
 def _normed(norm, part, h):
@@ -68,8 +68,9 @@ class Block:
         out = {s.mixer_prefix + k: v for k, v in self.mixer.params().items()}
         if self.ffn is not None:
             out.update({s.ffn_prefix + k: v for k, v in self.ffn.params().items()})
-        (norm_param,) = self.mixer_norm.params().values()
-        out[s.mixer_norm_name] = norm_param
+        norm = norm_params(self.mixer_norm, s.mixer_norm_name)
+        out.update(norm)
+        norm_param = norm[s.mixer_norm_name]
         width = norm_param.shape
         if s.mixer_scale_name is not None:
             out[s.mixer_scale_name] = Param(width, role="vector", mean=1.0)
@@ -77,23 +78,23 @@ class Block:
             # (a layer without a feed-forward: a checkpoint may still carry the scale that would follow one)
             out[s.ffn_scale_name] = Param(width, role="vector", mean=1.0, optional=self.ffn is None)
         if self.ffn is not None and self.ffn_norm is not None:
-            (norm_param,) = self.ffn_norm.params().values()
-            out[s.ffn_norm_name] = norm_param
+            out.update(norm_params(self.ffn_norm, s.ffn_norm_name))
         elif self.ffn is not None:
             pass  # an arrangement in which the feed-forward reads the mixer's norm
         elif s.ffn_norm_name is not None:
             # a layer without a feed-forward: a checkpoint may still carry the norm that would precede one
-            out[s.ffn_norm_name] = Param(norm_param.shape, role="vector", optional=True, mean=norm_param.mean)
+            for name, param in norm_params(self.mixer_norm, s.ffn_norm_name).items():
+                out[name] = Param(param.shape, role=param.role, optional=True, mean=param.mean)
         return out
 
     def load(self, get):
         s = self.spec
         self.mixer.load(lambda name: get(s.mixer_prefix + name))
-        self.mixer_norm.load(lambda _name: get(s.mixer_norm_name))
+        load_norm(self.mixer_norm, s.mixer_norm_name, get)
         if self.ffn is not None:
             self.ffn.load(lambda name: get(s.ffn_prefix + name))
             if self.ffn_norm is not None:
-                self.ffn_norm.load(lambda _name: get(s.ffn_norm_name))
+                load_norm(self.ffn_norm, s.ffn_norm_name, get)
         if s.mixer_scale_name is not None:
             self.mixer_scale = get(s.mixer_scale_name)
         if s.ffn_scale_name is not None and self.ffn is not None:

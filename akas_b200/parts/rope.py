@@ -10,9 +10,21 @@ and shared by every layer with the same encoding.
 
 from __future__ import annotations
 
+import math
+
 import torch
 
 from .base import Part, register_position
+
+
+def slow_long_waves(freq: torch.Tensor, factor: float, low: float, high: float, original: float) -> torch.Tensor:
+    """The rates of rotary pairs with long waves slowed (float64, on the host): with wavelength l = 2 pi / f a pair keeps
+    f where l < original / high, gets f / factor where l > original / low, and in between
+    (1 - s) f / factor + s f with s = (original / l - low) / (high - low)."""
+    wave = 2.0 * math.pi / freq
+    s = (original / wave - low) / (high - low)
+    blended = (1.0 - s) * freq / factor + s * freq
+    return torch.where(wave > original / low, freq / factor, torch.where(wave < original / high, freq, blended))
 
 
 class Rope(Part):
@@ -24,8 +36,12 @@ class Rope(Part):
         if rotary % 2 or rotary > spec.head_dim or rotary <= 0:
             raise ValueError(f"rotary_dim {rotary} must be even and at most head_dim {spec.head_dim}")
         i = torch.arange(rotary // 2, dtype=torch.float64)
-        self.inv_freq = (torch.tensor(float(spec.theta), dtype=torch.float64) ** (-2.0 * i / rotary)).to(runtime.device)
-        self.key = ("rope", rotary, float(spec.theta))  # the tables are the same for both pairings
+        freq = torch.tensor(float(spec.theta), dtype=torch.float64) ** (-2.0 * i / rotary)
+        scaling = getattr(spec, "scaling", None)
+        if scaling is not None:
+            freq = slow_long_waves(freq, *scaling)
+        self.inv_freq = freq.to(runtime.device)
+        self.key = ("rope", rotary, float(spec.theta), scaling)  # the tables are the same for both pairings
         self.interleaved = bool(getattr(spec, "interleaved", False))
 
     def tables(self, ctx):
