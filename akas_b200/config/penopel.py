@@ -142,13 +142,13 @@ class PenopelConfig:
         _int(where, m, "vdim")
         _number(where, m, "scale")
         _rot(where, m, dim)
-        if "kv_from" in m:
+        if m.get("kv_from") is not None:
             j = m["kv_from"]
             if type(j) is not int or not 0 <= j < index:
                 raise ConfigError(f"{where}.kv_from {j!r} must name an earlier layer")
             other = listed[j]
             theirs = other.get("mixer") if isinstance(other, Mapping) else None
-            if other.get("type") != "attention" or not isinstance(theirs, Mapping) or "kv_from" in theirs:
+            if other.get("type") != "attention" or not isinstance(theirs, Mapping) or theirs.get("kv_from") is not None:
                 raise ConfigError(f"{where}.kv_from {j}: that layer is no attention layer with keys and values of its own")
             for key in ("kv_heads", "dim", "vdim", "rot"):
                 if theirs.get(key) != m.get(key):
@@ -203,7 +203,7 @@ class PenopelConfig:
             names = {"q_proj.weight": "q", "k_proj.weight": "k", "v_proj.weight": "v", "out_proj.weight": "o"}
             return AttentionSpec(
                 c, m["heads"], m["kv_heads"], m["dim"], position=_rope(m["dim"], rot, rot["dims"], interleaved=False),
-                scale=float(m["scale"]), v_head_dim=m["vdim"], sink=True, bias=True, own_kv="kv_from" not in m, names=names,
+                scale=float(m["scale"]), v_head_dim=m["vdim"], sink=True, bias=True, own_kv=m.get("kv_from") is None, names=names,
             )
         mask = m.get("mask")
         return LatentAttentionSpec(

@@ -39,6 +39,16 @@ _SIGNATURES = {
         "akas_add_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "akas_polynorm": [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "akas_scaled_add": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p],
+        "akas_dynamic_tanh": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "akas_gated_activation": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                  c_int, c_void_p],
+    },
+    "latent": {
+        "akas_latent_norm_store": [c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                                   c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                   c_void_p],
+        "akas_head_linear": [c_void_p, c_longlong, c_void_p, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_void_p,
+                             c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
     },
     "moe": {
         "akas_moe_route": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
@@ -71,16 +81,17 @@ _SIGNATURES = {
     "attention_general": {
         "akas_qk_norm_store": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_void_p, c_float,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                               c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+                               c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
+                               c_void_p, c_void_p],
         "akas_attention_general": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_int,
                                    c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
-                                   c_int, c_int, c_int, c_void_p, c_float, c_longlong, c_void_p],
+                                   c_int, c_int, c_int, c_void_p, c_float, c_longlong, c_longlong, c_void_p],
     },
     "attention_general_tc": {
         "akas_attention_general_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float,
                                       c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int,
                                       c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_longlong, c_void_p, c_int,
-                                      c_void_p],
+                                      c_longlong, c_void_p],
         "akas_attention_general_tc_takes": [c_int, c_int],
     },
     "moe_grouped": {
@@ -225,6 +236,7 @@ _PART_FILES = {
     "recurrent": lambda dtype: ["recurrent"],
     "moe": lambda dtype: ["moe"] + (["moe_grouped"] if dtype == torch.bfloat16 else []),
     "rope": lambda dtype: ["rope"],
+    "latent": lambda dtype: ["latent"],
 }
 
 
@@ -1315,10 +1327,16 @@ def decay_scan(q, k, v, decay, state, cu_seqlens, slots, heads, dim, vdim, q_sca
 
 @_flushes
 def qk_norm_store(q, k, v, heads, kv_heads, dim, vdim, q_weight, k_weight, eps, k_pool, v_pool, block_table,
-                  seq_of_token, positions, page_size, write=True, cos=None, sin=None, interleaved=False):
+                  seq_of_token, positions, page_size, write=True, cos=None, sin=None, interleaved=False,
+                  q_bias=None, k_bias=None, v_bias=None):
     n = q.shape[0]
-    if not (q.dtype == k.dtype == v.dtype == k_pool.dtype == v_pool.dtype):
-        raise TypeError("qk_norm_store: q, k, v and the pages must have one dtype")
+    if not (q.dtype == k.dtype == v.dtype) or k_pool.dtype != v_pool.dtype:
+        raise TypeError("qk_norm_store: q, k, v must have one dtype, and so must the pages")
+    if q.dtype != k_pool.dtype and q.dtype != torch.float32:
+        raise TypeError("qk_norm_store: q, k, v come in the pages' dtype or as float32 results of a product")
+    for bias, size in ((q_bias, heads * dim), (k_bias, kv_heads * dim), (v_bias, kv_heads * vdim)):
+        if bias is not None and (bias.dtype != torch.float32 or bias.numel() != size or not bias.is_contiguous()):
+            raise ValueError("qk_norm_store: a bias is a dense float32 vector with one number per channel")
     rot = 0
     if cos is not None:
         rot = 2 * cos.shape[1]
@@ -1326,11 +1344,12 @@ def qk_norm_store(q, k, v, heads, kv_heads, dim, vdim, q_weight, k_weight, eps, 
             raise ValueError("qk_norm_store: rotary tables must be float32 [N, rot / 2] with rot <= dim")
         _dense(cos, "cos"), _dense(sin, "sin")
     (qp, ldq), (kp, ldk), (vp, ldv) = _rows(q, "q"), _rows(k, "k"), _rows(v, "v")
-    out = torch.empty((n, heads * dim), dtype=q.dtype, device=q.device)
+    out = torch.empty((n, heads * dim), dtype=k_pool.dtype, device=q.device)
     _check(_fn("attention_general", "akas_qk_norm_store")(
         qp, ldq, kp, ldk, vp, ldv, _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(out), _ptr(k_pool), _ptr(v_pool),
         _ptr(block_table), block_table.shape[1], _ptr(seq_of_token), _ptr(positions), page_size, n, heads, kv_heads, dim, vdim,
-        int(bool(write)), _code(q), _ptr(cos), _ptr(sin), rot, int(bool(interleaved)), _stream()), "qk_norm_store")
+        int(bool(write)), _code(k_pool), _ptr(cos), _ptr(sin), rot, int(bool(interleaved)), _code(q), _ptr(q_bias), _ptr(k_bias),
+        _ptr(v_bias), _stream()), "qk_norm_store")
     return out
 
 
@@ -1347,9 +1366,16 @@ general_splits = os.environ.get("AKAS_B200_GENERAL_SPLITS", "1") != "0"  # 0: a 
 
 @_flushes
 def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, scale, window, keep_first, softcap,
-                      r1, r2, sink, gate, page_size, ctx=None, sinks=None, out=None, out_scale=1.0):
+                      r1, r2, sink, gate, page_size, ctx=None, sinks=None, out=None, out_scale=1.0, values_in_keys=0):
+    """``values_in_keys`` = V > 0: a key's row holds its value too, as its first V channels; ``v_pool`` is not read."""
     n = q.shape[0]
-    kh, d, vd = k_pool.shape[1], k_pool.shape[3], v_pool.shape[3]
+    kh, d = k_pool.shape[1], k_pool.shape[3]
+    if values_in_keys:
+        if not 0 < values_in_keys <= d:
+            raise ValueError("attention_general: the values are the first channels of the keys' rows")
+        v_pool, vd, vpitch = k_pool, int(values_in_keys), d
+    else:
+        vd = vpitch = v_pool.shape[3]
     heads = q.shape[1] // d
     _dense(q, "q")
     if q.dtype != k_pool.dtype or (gate is not None and gate.dtype != q.dtype):
@@ -1368,7 +1394,8 @@ def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, s
     singles = n  # tokens at the front that are left to the kernel for any sizes
     lens = getattr(ctx, "query_lens", ()) if ctx is not None else ()
     if (general_attention == "mma" and q.dtype == torch.bfloat16 and lens
-            and ldo % 2 == 0 and op % 4 == 0 and _fn("attention_general_tc", "akas_attention_general_tc_takes")(d, vd)):
+            and ldo % 2 == 0 and op % 4 == 0 and vpitch % 8 == 0
+            and _fn("attention_general_tc", "akas_attention_general_tc_takes")(d, vd)):
         # The single tokens at the step's front (decoding requests) as one launch whose blocks hold the query heads of
         # a key/value head; then the requests from the first that brings more, as 64-query tiles. The kernel finds its
         # tiles from cu_seqlens and addresses block tables by request: both start at the launch's first request.
@@ -1386,13 +1413,104 @@ def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, s
                 err = _fn("attention_general_tc", "akas_attention_general_tc")(
                     _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table[start:]), block_table.shape[1],
                     _ptr(ctx.cu_seqlens[start:]), _ptr(positions), op, *options, tiles, heads, kh, d, vd, requests,
-                    packed, *tail, _ptr(partial), splits, _stream())
+                    packed, *tail, _ptr(partial), splits, vpitch, _stream())
                 _check(err, "attention_general (tensor cores)")
             singles = 0
     if singles:
         _check(_fn("attention_general", "akas_attention_general")(
             _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token), _ptr(positions),
-            op, *options, singles, heads, kh, d, vd, _code(q), *tail, _stream()), "attention_general")
+            op, *options, singles, heads, kh, d, vd, _code(q), *tail, vpitch, _stream()), "attention_general")
+    return out
+
+
+# --------------------------------------------------------------------------- latent attention, norms without sums
+
+
+@_flushes
+def dynamic_tanh(x, alpha, weight, shift, out_dtype, rows=None):
+    """tanh(alpha * x) * weight + shift per element of float32 x [N, C]; ``rows``: int32 indices of the rows to take."""
+    c = x.shape[-1]
+    if x.dtype != torch.float32 or alpha.dtype != torch.float32 or weight.numel() != c or shift.numel() != c:
+        raise ValueError("dynamic_tanh takes float32 x [N, C], a float32 alpha and vectors of C numbers")
+    _dense(x, "x")
+    m = rows.numel() if rows is not None else x.numel() // c
+    out = torch.empty((m, c) if rows is not None else x.shape, dtype=out_dtype, device=x.device)
+    _check(_fn("elementwise", "akas_dynamic_tanh")(_ptr(x), _ptr(alpha), _ptr(weight), _ptr(shift), _ptr(out), _ptr(rows), m, c,
+                                                  _CODE[out_dtype], _stream()), "dynamic_tanh")
+    return out
+
+
+_ACTIVATIONS = {"gelu_tanh": 0, "silu": 1}
+
+
+@_flushes
+def gated_activation(gate_up, width, bias, activation, out_dtype, residual=None, residual_bias=None):
+    """act(g + b_g) * (u + b_u) of a float32 product's rows [g | u]; with ``residual`` (float32 [N, C]) the same launch
+    adds ``residual_bias`` [C] to it in place: the bias of the product that will accumulate into that stream."""
+    n = gate_up.shape[0]
+    if gate_up.dtype != torch.float32 or gate_up.shape[1] < 2 * width:
+        raise ValueError("gated_activation takes a float32 product [N, >= 2 width]")
+    if activation not in _ACTIVATIONS:
+        raise ValueError(f"unknown activation {activation!r}")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != 2 * width):
+        raise ValueError("gated_activation: bias must be float32 [2 width]")
+    gp, ld = _rows(gate_up, "gate_up")
+    out = torch.empty((n, width), dtype=out_dtype, device=gate_up.device)
+    c = 0
+    if residual is not None:
+        c = residual.shape[1]
+        if (residual.dtype != torch.float32 or not residual.is_contiguous() or residual.shape[0] != n
+                or residual_bias is None or residual_bias.dtype != torch.float32 or residual_bias.numel() != c):
+            raise ValueError("gated_activation: residual must be dense float32 [N, C] with a float32 bias [C]")
+    _check(_fn("elementwise", "akas_gated_activation")(gp, ld, _ptr(bias), _ptr(out), n, width, _ACTIVATIONS[activation],
+                                                      _CODE[out_dtype], _ptr(residual), _ptr(residual_bias), c, _stream()),
+           "gated_activation")
+    return out
+
+
+@_flushes
+def latent_norm_store(proj, q_rank, kv_rank, rot, q_weight, kv_weight, eps, cos, sin, interleaved, pool, block_table,
+                      seq_of_token, positions, page_size, write=True):
+    n = proj.shape[0]
+    if proj.dtype != torch.float32 or proj.shape[1] < q_rank + kv_rank + rot:
+        raise ValueError("latent_norm_store takes the float32 product [N, >= q_rank + kv_rank + rot]")
+    if pool.shape[1] != 1 or pool.shape[3] != kv_rank + rot or not pool.is_contiguous():
+        raise ValueError("latent_norm_store: pages are [pages, 1, page, kv_rank + rot]")
+    if q_weight.numel() != q_rank or kv_weight.numel() != kv_rank:
+        raise ValueError("latent_norm_store: one norm weight per latent channel")
+    if cos is not None:
+        if not rot or cos.dtype != torch.float32 or cos.shape != (n, rot // 2) or sin.shape != cos.shape:
+            raise ValueError("latent_norm_store: rotary tables must be float32 [N, rot / 2]")
+        _dense(cos, "cos"), _dense(sin, "sin")
+    pp, ld = _rows(proj, "proj")
+    out = torch.empty((n, q_rank), dtype=pool.dtype, device=proj.device)
+    _check(_fn("latent", "akas_latent_norm_store")(
+        pp, ld, q_rank, kv_rank, rot, _ptr(q_weight), _ptr(kv_weight), float(eps), _ptr(cos), _ptr(sin), int(bool(interleaved)),
+        _ptr(out), _ptr(pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token), _ptr(positions), page_size, n,
+        int(bool(write)), _code(pool), _stream()), "latent_norm_store")
+    return out
+
+
+@_flushes
+def head_linear(x, w, heads, gate=None, cos=None, sin=None, interleaved=False):
+    n = x.shape[0]
+    h, o, k = w.shape
+    if h != heads or x.dtype != w.dtype or not w.is_contiguous() or x.shape[1] % heads or x.shape[1] // heads < k:
+        raise ValueError("head_linear takes x [N, heads * (K + T)] and dense w [heads, O, K] of one dtype")
+    t = x.shape[1] // heads - k
+    if cos is not None:
+        if not t or cos.dtype != torch.float32 or cos.shape != (n, t // 2) or sin.shape != cos.shape:
+            raise ValueError("head_linear: rotary tables must be float32 [N, T / 2]")
+        _dense(cos, "cos"), _dense(sin, "sin")
+    xp, ldx = _rows(x, "x")
+    gp, ldg, gcode = None, 0, _F32
+    if gate is not None:
+        if gate.shape != (n, heads * o):
+            raise ValueError("head_linear: gate must be [N, heads * O]")
+        (gp, ldg), gcode = _rows(gate, "gate"), _code(gate)
+    out = torch.empty((n, heads * (o + t)), dtype=x.dtype, device=x.device)
+    _check(_fn("latent", "akas_head_linear")(xp, ldx, _ptr(w), _ptr(out), out.stride(0), gp, ldg, gcode, _ptr(cos), _ptr(sin),
+                                            int(bool(interleaved)), n, heads, o, k, t, _code(x), _stream()), "head_linear")
     return out
 
 

@@ -523,9 +523,12 @@ def _activation(z, kind):
     raise ValueError(f"unknown activation {kind!r}")
 
 
-def gated_activation(gate_up, width, bias, activation, out_dtype):
+def gated_activation(gate_up, width, bias, activation, out_dtype, residual=None, residual_bias=None):
     """act(g + b_g) * (u + b_u) for float32 gate_up [N, >= 2 width] whose first ``width`` columns are g and whose next
-    are u; bias float32 [2 width] (b_g then b_u) or None -> [N, width] in ``out_dtype``, rounded once."""
+    are u; bias float32 [2 width] (b_g then b_u) or None -> [N, width] in ``out_dtype``, rounded once. With
+    ``residual`` (float32 [N, C]), ``residual_bias`` [C] is added to it in place."""
+    if residual is not None:
+        residual.add_(residual_bias)
     g, u = gate_up[:, :width].to(torch.float32), gate_up[:, width : 2 * width].to(torch.float32)
     if bias is not None:
         g, u = g + bias[:width], u + bias[width:]

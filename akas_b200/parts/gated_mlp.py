@@ -3,8 +3,8 @@ W_down (act(W_gate x + b_gate) * (W_up x + b_up)) + b_down.
 
 W_gate and W_up are stacked at load so that one product feeds the activation. That product leaves float32; the
 biases, the activation and the product of the two halves are float32 (``ops.gated_activation``), rounded once to the
-compute dtype as the down product's operand. The down bias is added to the float32 residual stream, which the down
-product then accumulates into.
+compute dtype as the down product's operand. The down bias is added to the float32 residual stream by the
+activation's launch; the down product then accumulates into that stream.
 """
 
 from __future__ import annotations
@@ -48,12 +48,14 @@ class GatedMLP(FeedForward):
     def forward(self, x, ctx, residual=None):
         ops = self.rt.ops
         gate_up = project(self.rt, x, self.w_gate_up, out_dtype=torch.float32)
-        act = ops.gated_activation(gate_up, self.spec.intermediate_size, self.bias_gate_up, self.spec.activation, self.rt.dtype)
+        more = {}
+        if residual is not None and self.bias_down is not None:
+            more = dict(residual=residual, residual_bias=self.bias_down)  # the same launch adds the last product's bias
+        act = ops.gated_activation(gate_up, self.spec.intermediate_size, self.bias_gate_up, self.spec.activation, self.rt.dtype,
+                                   **more)
         if residual is None:
             out = project(self.rt, act, self.w_down, out_dtype=torch.float32)
             return ops.add_bias(out, self.bias_down, self.rt.dtype) if self.bias_down is not None else out.to(self.rt.dtype)
-        if self.bias_down is not None:
-            residual = ops.add_bias(residual, self.bias_down)
         return project(self.rt, act, self.w_down, residual=residual)
 
 
