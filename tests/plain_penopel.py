@@ -110,7 +110,7 @@ def latent_attention(h, w, p, m, eps):
     k_rot = rotate(down[:, rank:].reshape(T, 1, R), rot, interleaved=True)[:, 0]
     k_plain = (c @ w[p + "uk"].T).reshape(T, H, D)
     v = (c @ w[p + "uv"].T).reshape(T, H, V)
-    size = m["mask"]["size"]
+    size = m["mask"]["size"] if m.get("mask") is not None else T + 1  # no mask: every earlier position
     out = torch.zeros(T, H, V, dtype=F)
     for i in range(T):
         lo = max(0, i - size + 1)
@@ -138,7 +138,7 @@ def forward(tokens, w, cfg, trace=None):
         p, m = f"l{i}.", entry["mixer"]
         h = dyt(x, w, p + "norm1")
         if entry["type"] == "attention":
-            if "kv_from" in m:
+            if m.get("kv_from") is not None:
                 x = x + attention(h, w, p + "mix.", m, kv=left[m["kv_from"]])
             else:
                 left[i] = keys_and_values(h, w, p + "mix.", m)
