@@ -39,6 +39,9 @@ def matrix_params(runner: ModelRunner) -> Dict[str, int]:
                     layers += value.numel()
                 elif isinstance(value, torch.Tensor) and value.dim() == 3 and value.dtype == runner.dtype:
                     s = part.spec
+                    if not hasattr(s, "top"):  # a matrix per head: a token passes through all of them
+                        layers += value.numel()
+                        continue
                     real = s.top * s.num_experts / (s.num_experts + s.num_identity)
                     layers += int(value[0].numel() * real)
     return dict(layers=layers, head=runner.model.head.numel())
@@ -66,6 +69,10 @@ def prefill_flops(runner: ModelRunner, tokens: int, start: int = 0) -> float:
             else:
                 pairs = tokens * start + tokens * (tokens + 1) / 2
             flops += 2.0 * pairs * spec.num_heads * (spec.head_dim + getattr(spec, "value_dim", spec.head_dim))
+        elif kind == "latent_attention":
+            # as computed: every head's query against the cached rows [latent, rotated part], weights times the latent
+            pairs = sum(min(start + i + 1, spec.window) for i in range(tokens)) if spec.window else tokens * start + tokens * (tokens + 1) / 2
+            flops += 2.0 * pairs * spec.num_heads * (2 * spec.kv_rank + spec.rope_dim)
         elif kind in ("gated_linear_attention", "gated_delta", "decayed_linear_attention"):
             # the matrix state: decay and rank-one update, read-out (and the delta rule's read before the update)
             per = 6.0 if kind == "gated_delta" else 4.0
@@ -87,8 +94,11 @@ def decode_bytes(runner: ModelRunner, contexts: Sequence[int]) -> float:
         spec = getattr(view, "spec", None)
         if spec is None:
             continue
-        if hasattr(spec, "num_kv_heads"):
-            per_token = spec.num_kv_heads * (spec.head_dim + (getattr(spec, "v_head_dim", None) or spec.head_dim)) * elem
+        if hasattr(spec, "num_kv_heads") or hasattr(spec, "width"):
+            if hasattr(spec, "width"):  # one row per token that is key and value of every head
+                per_token = spec.width * elem
+            else:
+                per_token = spec.num_kv_heads * (spec.head_dim + (getattr(spec, "v_head_dim", None) or spec.head_dim)) * elem
             for c in contexts:
                 total += per_token * (min(c, spec.window + getattr(spec, "keep_first", 0)) if spec.window else c)
         else:
@@ -464,6 +474,31 @@ def girelix_shape_config(name: str) -> dict:
                 layers=[entry] * len(lfm2.layer_kinds))
 
 
+# Penopel at LFM2's layer sizes: the same width, vocabulary and number of layers, a gated feed-forward of LFM2's width in
+# every layer. Of every four layers two are latent attention (a head per 128 channels of the width, 64 plain and 32
+# rotated channels a head, a key/value latent of 96, so a cached row of 128 numbers; a window of 1,024), one is
+# attention with LFM2's head counts, and one reads that layer's cache with queries of its own.
+def penopel_shape_config(name: str) -> dict:
+    lfm2 = config_from_shape(name)
+    c, ff3 = lfm2.hidden_size, lfm2.feed_forward_size
+    rot = dict(base=500000.0, dims=lfm2.head_dim, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192))
+    attention = dict(heads=lfm2.num_attention_heads, kv_heads=lfm2.num_key_value_heads, dim=lfm2.head_dim, vdim=lfm2.head_dim,
+                     scale=lfm2.head_dim ** -0.5, rot=rot)
+    latent = dict(heads=c // 128, dim=64, rot_dim=32, vdim=64, q_rank=3 * c // 8, kv_rank=96, scale=96 ** -0.5,
+                  mask=dict(size=1024), rot=dict(base=1000000.0, dims=32))
+    mlp = dict(kind="dense", ff=ff3)
+    layers = []
+    for i in range(len(lfm2.layer_kinds)):
+        if i % 4 == 1:
+            layers.append(dict(type="attention", mixer=attention, mlp=mlp))
+        elif i % 4 == 3:
+            layers.append(dict(type="attention", mixer=dict(attention, kv_from=i - 2), mlp=mlp))
+        else:
+            layers.append(dict(type="latent_attention", mixer=latent, mlp=mlp))
+    return dict(architecture="Penopel", width=c, vocab=lfm2.vocab_size, norm=dict(eps=1e-5), embedding=dict(scale=float(c) ** 0.5),
+                logit_softcap=30.0, layers=layers)
+
+
 def config_from_shape(name: str):
     from .config import config_from_dict
 
@@ -489,7 +524,8 @@ def compare_designs(shape: str = "1.2b", prompt: int = 2048, batches=(8, 64), st
         print(f"[compare] {what}", file=sys.stderr, flush=True)
 
     rows = []
-    shapes = {"lfm2": shape_config, "gigusun": gigusun_shape_config, "girelix": girelix_shape_config}
+    shapes = {"lfm2": shape_config, "gigusun": gigusun_shape_config, "girelix": girelix_shape_config,
+              "penopel": penopel_shape_config}
     for design, data in ((name, shapes[name](shape)) for name in designs):
         say(f"{design} {shape}: writing random weights")
         model_config = config_from_dict(data)

@@ -97,6 +97,22 @@ template <typename T> struct Vec;
 template <> struct Vec<float> { static constexpr int N = 4; };
 template <> struct Vec<bf16> { static constexpr int N = 8; };
 
+// The activation of a gated feed-forward's read-out, act(g), from the special-function unit: act 0 is silu,
+// g * sigmoid(g); act 1 the tanh form of gelu, 0.5 g (1 + tanh(y)) with y = sqrt(2 / pi) (g + 0.044715 g^3), which is
+// g * sigmoid(2 y). (The fast division and exponential: the result is rounded to bfloat16 right after.)
+#define AKAS_ACT_SILU 0
+#define AKAS_ACT_GELU_TANH 1
+__device__ __forceinline__ float gate_activation_fast(float g, int act) {
+  const float y = act == AKAS_ACT_GELU_TANH ? 1.5957691216057308f * fmaf(0.044715f * g * g, g, g) : g;
+  return __fdividef(g, 1.f + __expf(-y));
+}
+
+// tanh(x) = 1 - 2 / (e^(2x) + 1) from the special-function unit: an absolute error of a few 1e-7, for results that are
+// rounded to bfloat16 next.
+__device__ __forceinline__ float tanh_fast(float x) {
+  return 1.f - __fdividef(2.f, __expf(fminf(2.f * x, 80.f)) + 1.f);
+}
+
 static inline int launch_status() { return (int)cudaGetLastError(); }
 
 // Programmatic dependent launch. Kernels of a decode step follow one another on one stream; a kernel

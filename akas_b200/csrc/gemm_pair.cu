@@ -143,7 +143,8 @@ __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.a
 template <int BN, int EPI, bool WIDE>
 __global__ void __launch_bounds__(THREADS)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                 const __grid_constant__ CUtensorMap map_y, int M, int N, int K, int F) {
+                 const __grid_constant__ CUtensorMap map_y, int M, int N, int K, int F, const float* __restrict__ bias,
+                 int act) {
   // N: channels of the product (for SWIGLU the stacked height 2F); a tile covers BN of them (SWIGLU: BN/2 gate
   // rows f0.. and BN/2 up rows F + f0..).
   using S = Shape<BN>;
@@ -279,6 +280,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         if (EPI == EPI_ACC || EPI == EPI_F32) {
           float v[32];
           tmem_load32(taddr + c, v);
+          if (bias != nullptr) {  // one number per output channel, added before anything is written
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] += n0 + c + i < N ? bias[n0 + c + i] : 0.f;
+          }
           // row `lane` of 128 bytes, its 16-byte units XORed with the row's number within eight (the 128-byte swizzle)
 #pragma unroll
           for (int j = 0; j < 8; ++j)
@@ -311,8 +316,16 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           float v[32], u[32];
           tmem_load32(taddr + c, v);
           tmem_load32(taddr + BN / 2 + c, u);
+          if (bias != nullptr) {  // [2F]: the gate rows' biases, then the up rows'
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __fdividef(v[i], 1.f + __expf(-v[i])) * u[i];  // the fast division: IEEE division cost more than the tile's loads
+            for (int i = 0; i < 32; ++i) {
+              const int f = n0 + c + i < F ? n0 + c + i : F - 1;
+              v[i] += bias[f];
+              u[i] += bias[F + f];
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = gate_activation_fast(v[i], act) * u[i];  // the fast division: IEEE division cost more than the tile's loads
           // row `lane` of 64 bytes, its 16-byte units XORed with bits 7-8 of the address (the 64-byte swizzle)
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -402,7 +415,7 @@ int cached_wide_map(CUtensorMap* out, const void* base, int rows, int K, int box
 }
 
 template <int BN, int EPI, bool WIDE>
-int launch(const void* x, const void* w, void* y, int M, int N, int K, cudaStream_t stream) {
+int launch(const void* x, const void* w, void* y, int M, int N, int K, const float* bias, int act, cudaStream_t stream) {
   constexpr int smem = Shape<BN>::SMEM;
   static int pairs_room[64] = {};
   int device = 0;
@@ -455,12 +468,12 @@ int launch(const void* x, const void* w, void* y, int M, int N, int K, cudaStrea
   attribute[1].val.programmaticStreamSerializationAllowed = 1;
   config.attrs = attribute;
   config.numAttrs = chained_launches_enabled() ? 2 : 1;
-  const cudaError_t e = cudaLaunchKernelEx(&config, gemm_pair_kernel<BN, EPI, WIDE>, map_x, map_w, map_y, M, N, K, F);
+  const cudaError_t e = cudaLaunchKernelEx(&config, gemm_pair_kernel<BN, EPI, WIDE>, map_x, map_w, map_y, M, N, K, F, bias, act);
   return e != cudaSuccess ? (int)e : launch_status();
 }
 
 template <int EPI>
-int launch_width(const void* x, const void* w, void* y, int M, int N, int K, cudaStream_t stream) {
+int launch_width(const void* x, const void* w, void* y, int M, int N, int K, const float* bias, int act, cudaStream_t stream) {
   // The tile width that finishes first by a count of the issuing thread's cycles: rounds over the pairs of SMs (a B200
   // has 74) times what a stage of eight products takes, which is the tensor cores' 131 cycles a product at 256 channels
   // and in proportion for narrower tiles, but never less than the 700 cycles it costs the one thread to issue eight
@@ -482,7 +495,7 @@ int launch_width(const void* x, const void* w, void* y, int M, int N, int K, cud
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
   }
 #define AKAS_PAIR_WIDTH(BN_) \
-  case BN_: return K % 64 == 0 ? launch<BN_, EPI, true>(x, w, y, M, N, K, stream) : launch<BN_, EPI, false>(x, w, y, M, N, K, stream);
+  case BN_: return K % 64 == 0 ? launch<BN_, EPI, true>(x, w, y, M, N, K, bias, act, stream) : launch<BN_, EPI, false>(x, w, y, M, N, K, bias, act, stream);
   switch (best) {
     AKAS_PAIR_WIDTH(256) AKAS_PAIR_WIDTH(192) AKAS_PAIR_WIDTH(128) AKAS_PAIR_WIDTH(64)
   }
@@ -496,19 +509,33 @@ int launch_width(const void* x, const void* w, void* y, int M, int N, int K, cud
 // 2 (swiglu, w the stacked [2F, K] gate and up matrices, N = 2F): y bfloat16 [M, F]. Returns 0, a CUDA error code, or 3000 + a driver
 // error from building a tensor map. K and the row pitch of y in bytes must be multiples of 16 bytes' worth of elements
 // (K % 8, N % 8 for bfloat16 y, N % 4 for float32 y, F % 8): TMA moves every operand.
-AKAS_API int akas_gemm_pair(const void* x, const void* w, void* y, int M, int N, int K, int epilogue, cudaStream_t stream) {
+static int pair_dispatch(const void* x, const void* w, void* y, int M, int N, int K, int epilogue, const float* bias, int act,
+                         cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || (uintptr_t)x % 16 || (uintptr_t)w % 16 || (uintptr_t)y % 16) return (int)cudaErrorInvalidValue;
   if (epilogue == EPI_SWIGLU && (N % 2 || (N / 2) % 8)) return (int)cudaErrorInvalidValue;
-  if (epilogue == EPI_BF16 && N % 8) return (int)cudaErrorInvalidValue;
+  if (epilogue == EPI_BF16 && (N % 8 || bias != nullptr)) return (int)cudaErrorInvalidValue;
   if ((epilogue == EPI_ACC || epilogue == EPI_F32) && N % 4) return (int)cudaErrorInvalidValue;
+  if (act != AKAS_ACT_SILU && act != AKAS_ACT_GELU_TANH) return (int)cudaErrorInvalidValue;
   switch (epilogue) {
-    case EPI_BF16: return launch_width<EPI_BF16>(x, w, y, M, N, K, stream);
-    case EPI_ACC: return launch_width<EPI_ACC>(x, w, y, M, N, K, stream);
-    case EPI_SWIGLU: return launch_width<EPI_SWIGLU>(x, w, y, M, N, K, stream);
-    case EPI_F32: return launch_width<EPI_F32>(x, w, y, M, N, K, stream);
+    case EPI_BF16: return launch_width<EPI_BF16>(x, w, y, M, N, K, nullptr, 0, stream);
+    case EPI_ACC: return launch_width<EPI_ACC>(x, w, y, M, N, K, bias, 0, stream);
+    case EPI_SWIGLU: return launch_width<EPI_SWIGLU>(x, w, y, M, N, K, bias, act, stream);
+    case EPI_F32: return launch_width<EPI_F32>(x, w, y, M, N, K, bias, 0, stream);
     default: return (int)cudaErrorInvalidValue;
   }
+}
+
+AKAS_API int akas_gemm_pair(const void* x, const void* w, void* y, int M, int N, int K, int epilogue, cudaStream_t stream) {
+  return pair_dispatch(x, w, y, M, N, K, epilogue, nullptr, AKAS_ACT_SILU, stream);
+}
+
+// The same with a float32 bias: one number per output channel for the float32 read-outs (1: y += product + bias), or,
+// for read-out 2, [2F] (the gate rows' biases, then the up rows') and the gate's activation (0 silu, 1 the tanh form of
+// gelu): y = act(gate + b_g) * (up + b_u).
+AKAS_API int akas_gemm_pair_bias(const void* x, const void* w, void* y, int M, int N, int K, int epilogue, const float* bias,
+                                 int act, cudaStream_t stream) {
+  return pair_dispatch(x, w, y, M, N, K, epilogue, bias, act, stream);
 }
 
 // 0 if no bounded wait of the kernel has ever run out on the current device (1: producer, 2: tensor cores,

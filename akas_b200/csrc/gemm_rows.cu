@@ -158,6 +158,8 @@ struct Shape {
   unsigned suspend_ns;  // how long a waiting thread may sleep before it looks at its barrier again
   int parts;          // blocks of a cluster that share a tile, one part of K each (1: no cluster)
   int part_blocks;    // 64-wide steps of K in a part (a multiple of G)
+  const float* bias;  // float32, or null: one number per output channel (float32 read-outs), or [2F] for the gated read-out
+  int act;            // the gated read-out's activation: 0 silu, 1 the tanh form of gelu
 };
 
 template <int EPI>
@@ -441,6 +443,10 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
               }
             }
           }
+          if ((EPI == EPI_ACC || EPI == EPI_F32) && sh.bias != nullptr) {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[i] += n0 + c + i < out_cols ? sh.bias[n0 + c + i] : 0.f;
+          }
           if (EPI == EPI_ACC || EPI == EPI_F32) {
             // row `lane` of 64 bytes, its 16-byte units XORed with bits 7-8 of the address (the 64-byte swizzle)
 #pragma unroll
@@ -451,8 +457,16 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
             if (SWIGLU) {
               float u[16];
               tmem_sum16(taddr + TN + c, W, acc_cols, u);
+              if (sh.bias != nullptr) {  // [2F]: the gate rows' biases, then the up rows'
 #pragma unroll
-              for (int i = 0; i < 16; ++i) v[i] = __fdividef(v[i], 1.f + __expf(-v[i])) * u[i];  // the fast division: IEEE division cost more than the tile's loads
+                for (int i = 0; i < 16; ++i) {
+                  const int f = n0 + c + i < sh.F ? n0 + c + i : sh.F - 1;
+                  v[i] += sh.bias[f];
+                  u[i] += sh.bias[sh.F + f];
+                }
+              }
+#pragma unroll
+              for (int i = 0; i < 16; ++i) v[i] = gate_activation_fast(v[i], sh.act) * u[i];  // the fast division: IEEE division cost more than the tile's loads
             }
             // row `lane` of 32 bytes, its two 16-byte units XORed with bit 7 of the address (the 32-byte swizzle)
 #pragma unroll
@@ -675,6 +689,10 @@ int launch_uncut(Kernel kernel, const void* x, const void* w, const CUtensorMap&
   return e != cudaSuccess ? (int)e : launch_status();
 }
 
+// The bias and the activation of the call under way (akas_gemm_rows_bias sets them around its dispatch).
+thread_local const float* t_bias = nullptr;
+thread_local int t_act = 0;
+
 template <int EPI>
 int launch(const void* x, const void* w, void* y, int M, int O, int K, bool dry, cudaStream_t stream) {
   auto kernel = gemm_rows_kernel<EPI>;
@@ -701,6 +719,8 @@ int launch(const void* x, const void* w, void* y, int M, int O, int K, bool dry,
     if (!plan(&sh, M, O, K, EPI, sms[device], budget[device], 1)) return 3999;
   }
   if (dry) return 0;
+  sh.bias = EPI == EPI_BF16 ? nullptr : t_bias;
+  sh.act = t_act;
   constexpr bool SWIGLU = EPI == EPI_SWIGLU;
   const int out_cols = SWIGLU ? O / 2 : O;
   CUtensorMap map_x, map_w, map_y;
@@ -784,6 +804,21 @@ int dispatch(const void* x, const void* w, void* y, int M, int O, int K, int epi
 // O % 4 for float32 y, F % 8), since TMA moves every operand.
 AKAS_API int akas_gemm_rows(const void* x, const void* w, void* y, int M, int O, int K, int epilogue, cudaStream_t stream) {
   return dispatch(x, w, y, M, O, K, epilogue, false, stream);
+}
+
+// The same with a float32 bias: one number per output channel for the float32 read-outs (1: y += product + bias), or,
+// for read-out 2, [2F] (the gate rows' biases, then the up rows') and the gate's activation (0 silu, 1 the tanh form of
+// gelu): y = act(gate + b_g) * (up + b_u).
+AKAS_API int akas_gemm_rows_bias(const void* x, const void* w, void* y, int M, int O, int K, int epilogue, const float* bias,
+                                 int act, cudaStream_t stream) {
+  if (act != AKAS_ACT_SILU && act != AKAS_ACT_GELU_TANH) return (int)cudaErrorInvalidValue;
+  if (epilogue == EPI_BF16 && bias != nullptr) return (int)cudaErrorInvalidValue;
+  t_bias = bias;
+  t_act = act;
+  const int err = dispatch(x, w, y, M, O, K, epilogue, false, stream);
+  t_bias = nullptr;
+  t_act = 0;
+  return err;
 }
 
 // 1 if akas_gemm_rows takes these sizes on the current device, else 0. Launches nothing.

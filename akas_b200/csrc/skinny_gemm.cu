@@ -66,7 +66,7 @@ constexpr int MAX_KSPLIT = 8, SPLIT_TILES = 4;  // parts of K; row tiles a clust
 constexpr int STAGE_BYTES = 16 * KC * 2;  // one box of [8 groups of k][16 rows][128 bytes], or (SwiGLU) two of 8 rows
 constexpr int THREADS = (CONSUMERS + 1) * 32;
 constexpr unsigned kSpinLimit = 1u << 22;  // try_wait calls before a wait gives up (each may block for a while)
-enum { IN_BF16 = 0, IN_NORM = 1 };
+enum { IN_BF16 = 0, IN_NORM = 1, IN_DYT = 2 };
 enum { OUT_BF16 = 0, OUT_F32 = 1, OUT_ACC = 2, OUT_SWIGLU = 3, OUT_CONV = 4 };
 // Bytes of a stage, stages of the ring and weight rows of a tile, by read-out: the convolution's three boxes of 8 rows
 // make a stage of 24 KB, and three of them leave room for two blocks on an SM.
@@ -82,7 +82,11 @@ struct ConvTail {
   float* state;             // [slots, L - 1, C]
   const int* seq_of_token;  // [M]: the request of a token, or -1 for padding
   const int* slots;         // [requests]: the state row of a request
-  int L, write;
+  int L, write;             // (gated read-out: L is the activation, 0 silu, 1 the tanh form of gelu)
+  // read-outs without a convolution: `bias` is one float32 per output channel (float32 read-outs: y = product + bias,
+  // or += for the accumulating one), or [2F] for the gated read-out (the gate rows' biases, then the up rows')
+  const float* in_shift;    // in_mode 2: the norm's shift [K]
+  const float* in_alpha;    // in_mode 2: the norm's slope, one number
 };
 
 __device__ int g_skinny_status = 0;  // 0, or the code of a wait that ran out (1: a full stage, 2: an empty stage)
@@ -182,7 +186,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
   if (GROUPED) {
     const int m0 = (item0 % groups) * NT * 8;
     if (rows) rows += m0;
-    else x_ = IN == IN_NORM ? (const void*)((const float*)x_ + (size_t)m0 * K) : (const void*)((const bf16*)x_ + (size_t)m0 * K);
+    else x_ = IN != IN_BF16 ? (const void*)((const float*)x_ + (size_t)m0 * K) : (const void*)((const bf16*)x_ + (size_t)m0 * K);
     const size_t width = OUT == OUT_SWIGLU ? O / 2 : OUT == OUT_CONV ? O / 3 : O;
     y_ = OUT == OUT_F32 || OUT == OUT_ACC ? (void*)((float*)y_ + m0 * width) : (void*)((bf16*)y_ + m0 * width);
     if (OUT == OUT_CONV) token_request += m0;
@@ -263,6 +267,33 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
       }
       cp_async_commit();
       cp_async_wait<0>();
+    } else if (IN == IN_DYT) {
+      // float32 residual rows -> bf16(tanh(alpha x) * w + b), element by element: a norm without sums. A warp takes
+      // 128-float blocks of k for every token, as below; the weights and shifts are fetched before the wait.
+      const int kblocks = (k_len + 127) / 128;
+      const float alpha = tail.in_alpha[0];
+      chain_wait();  // from here on the kernel reads what its predecessor wrote
+      for (int b0 = warp; b0 < kblocks; b0 += CONSUMERS) {
+        const int k = b0 * 128 + lane * 4;
+        if (k >= k_len) continue;
+        const float4 w = *reinterpret_cast<const float4*>(norm_w + k0 + k);
+        const float4 sh = *reinterpret_cast<const float4*>(tail.in_shift + k0 + k);
+        float4 v[NT * 8];
+#pragma unroll
+        for (int m = 0; m < NT * 8; ++m) {
+          const float* src = (const float*)x_ + (size_t)(m < M ? (rows ? rows[m] : m) : 0) * K + k0;
+          v[m] = m < M ? *reinterpret_cast<const float4*>(src + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int m = 0; m < NT * 8; ++m) {
+          const float4 a = v[m];
+          uint2 packed;
+          packed.x = pack_bf16(fmaf(tanh_fast(alpha * a.x), w.x, sh.x), fmaf(tanh_fast(alpha * a.y), w.y, sh.y));
+          packed.y = pack_bf16(fmaf(tanh_fast(alpha * a.z), w.z, sh.z), fmaf(tanh_fast(alpha * a.w), w.w, sh.w));
+          if (m >= M) packed = make_uint2(0u, 0u);
+          *reinterpret_cast<uint2*>(xs + (size_t)m * XS + k) = packed;
+        }
+      }
     } else {
       // float32 residual rows -> bf16(x * norm weight), with the sum of x^2 on the way. A warp takes 128-float blocks
       // of k (blocks warp, warp + 8, ...) for every token, two blocks a pass: the pass's 16 loads per lane (8 tokens x
@@ -478,11 +509,16 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
           *out = __float2bfloat16_rn(cq * sum);
         } else if (OUT == OUT_SWIGLU) {
           const int f = tile * 8 + row;
-          if (f < F) ((bf16*)y_)[(size_t)m * F + f] = __float2bfloat16_rn(v / (1.f + expf(-v)) * u);
+          if (f < F) {
+            if (tail.bias != nullptr) { v += tail.bias[f]; u += tail.bias[F + f]; }
+            const float y = tail.L == AKAS_ACT_GELU_TANH ? 1.5957691216057308f * fmaf(0.044715f * v * v, v, v) : v;
+            ((bf16*)y_)[(size_t)m * F + f] = __float2bfloat16_rn(v / (1.f + expf(-y)) * u);
+          }
         } else {
           const int o = tile * 16 + row;
           if (o >= O) continue;
           const size_t at = (size_t)m * O + o;
+          if (OUT != OUT_BF16 && tail.bias != nullptr) v += tail.bias[o];
           if (OUT == OUT_BF16) ((bf16*)y_)[at] = __float2bfloat16_rn(v);
           else if (OUT == OUT_F32) ((float*)y_)[at] = v;
           else ((float*)y_)[at] = before + v;
@@ -539,6 +575,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
             }
             if (IN == IN_NORM) v *= 1.f / sqrtf(ss / (float)K + eps);
             const size_t at = (size_t)m * O + o;
+            if (OUT != OUT_BF16 && tail.bias != nullptr) v += tail.bias[o];
             if (OUT == OUT_BF16) ((bf16*)y_)[at] = __float2bfloat16_rn(v);
             else if (OUT == OUT_F32) ((float*)y_)[at] = v;
             else ((float*)y_)[at] = before[n] + v;
@@ -756,8 +793,19 @@ static int skinny_dispatch(const void* x, const int* rows, const float* norm_w, 
                            void* y, int M, int O, int K, int in_mode, int out_mode, const ConvTail& tail, cudaStream_t stream) {
   if (M <= 0 || O <= 0) return 0;
   if (M > 16 || K <= 0 || K % 64 || (out_mode == OUT_SWIGLU && O % 2) || (out_mode == OUT_CONV && O % 3)) return (int)cudaErrorInvalidValue;
-  if (in_mode == IN_NORM && norm_w == nullptr) return (int)cudaErrorInvalidValue;
+  if (in_mode != IN_BF16 && norm_w == nullptr) return (int)cudaErrorInvalidValue;
   if ((uintptr_t)W % 16 || (uintptr_t)x % 16) return (int)cudaErrorInvalidValue;  // TMA and 16-byte loads
+  if (in_mode == IN_DYT) {
+    // the norm without sums in front of the plain, the float32 and the gated read-outs (what its models use)
+    if (tail.in_shift == nullptr || tail.in_alpha == nullptr) return (int)cudaErrorInvalidValue;
+    const int groups = M <= 8 ? 1 : 2;
+    switch (out_mode) {
+      case OUT_BF16: return launch_one<1, IN_DYT, OUT_BF16>((O + 15) / 16, x, rows, norm_w, eps, 0, W, y, M, O, K, tail, groups, stream);
+      case OUT_F32: return launch_one<1, IN_DYT, OUT_F32>((O + 15) / 16, x, rows, norm_w, eps, 0, W, y, M, O, K, tail, groups, stream);
+      case OUT_SWIGLU: return launch_one<1, IN_DYT, OUT_SWIGLU>((O / 2 + 7) / 8, x, rows, norm_w, eps, 0, W, y, M, O, K, tail, groups, stream);
+      default: return (int)cudaErrorInvalidValue;
+    }
+  }
   // 9 to 16 tokens: as two groups of 8 on the kernel for 8, whose blocks then come in pairs that read the same weights
   // (the second mostly from the L2), rather than on the kernel for 16, whose activations leave room for one block per
   // SM only (AKAS_B200_SKINNY_GROUPS=0: that kernel).
@@ -776,6 +824,20 @@ AKAS_API int akas_skinny_gemm(const void* x, const int* rows, const float* norm_
                               cudaStream_t stream) {
   if (out_mode < OUT_BF16 || out_mode > OUT_SWIGLU) return (int)cudaErrorInvalidValue;
   return skinny_dispatch(x, rows, norm_w, eps, zero_centered, W, y, M, O, K, in_mode, out_mode, ConvTail{}, stream);
+}
+
+// The same with more: in_mode 2, the input rows through a norm without sums, bf16(tanh(alpha x) * norm_w + shift), in
+// front of out modes 0, 1 and 3; a float32 bias on the float32 read-outs (one number per output channel: y = product +
+// bias, or += for the accumulating one) or on the gated read-out ([2F], with `act` 0 silu or 1 the tanh form of gelu:
+// y = act(gate + b_g) * (up + b_u)).
+AKAS_API int akas_skinny_gemm_more(const void* x, const int* rows, const float* norm_w, const float* shift, const float* alpha,
+                                   const void* W, void* y, int M, int O, int K, int in_mode, int out_mode, const float* bias,
+                                   int act, cudaStream_t stream) {
+  if (out_mode < OUT_BF16 || out_mode > OUT_SWIGLU || in_mode == IN_NORM) return (int)cudaErrorInvalidValue;
+  if (act != AKAS_ACT_SILU && act != AKAS_ACT_GELU_TANH) return (int)cudaErrorInvalidValue;
+  if (out_mode == OUT_BF16 && bias != nullptr) return (int)cudaErrorInvalidValue;
+  const ConvTail tail{nullptr, bias, nullptr, nullptr, nullptr, act, 0, shift, alpha};
+  return skinny_dispatch(x, rows, norm_w, 0.f, 0, W, y, M, O, K, in_mode, out_mode, tail, stream);
 }
 
 // The in projection of a gated short convolution and the convolution itself, for a decode step: W bfloat16 [3C, K]

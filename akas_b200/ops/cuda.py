@@ -156,10 +156,12 @@ _SIGNATURES = {
     },
     "gemm_pair": {
         "akas_gemm_pair": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "akas_gemm_pair_bias": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
         "akas_gemm_pair_status": [],
     },
     "gemm_rows": {
         "akas_gemm_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "akas_gemm_rows_bias": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
         "akas_gemm_rows_takes": [c_int, c_int, c_int, c_int],
         "akas_gemm_rows_status": [],
     },
@@ -174,6 +176,8 @@ _SIGNATURES = {
                              c_int, c_int, c_void_p],
         "akas_skinny_gemm_conv": [c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                   c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "akas_skinny_gemm_more": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                  c_int, c_int, c_void_p, c_int, c_void_p],
         "akas_skinny_gemm_status": [],
     },
     "decode_chain": {
@@ -502,8 +506,12 @@ def _workspace(device):
     return ws
 
 
-def linear(x, w, out_dtype=None, residual=None):
-    """x [N, K] times w [O, K] transposed. With ``residual`` (float32 [N, O]) the product is added into it."""
+def linear(x, w, out_dtype=None, residual=None, bias=None):
+    """x [N, K] times w [O, K] transposed. With ``residual`` (float32 [N, O]) the product is added into it. ``bias``
+    (float32 [O]) rides in the read-out of a product that is added into the residual; elsewhere it is added by a
+    kernel of its own, before the one rounding."""
+    if bias is not None:
+        return _linear_bias(x, w, out_dtype, residual, bias)
     n, k = x.shape
     o = w.shape[0]
     if w.shape[1] != k:
@@ -562,6 +570,95 @@ def linear(x, w, out_dtype=None, residual=None):
     ws = _workspace(x.device)
     _check(_fn("gemm_bf16", "akas_gemm_bf16")(_ptr(x), _ptr(w), _ptr(out), n, o, k, out_f32, acc, _ptr(ws),
                                              ws.numel(), _stream()), f"bfloat16 product [{n}x{k}] x [{o}x{k}]^T")
+    return out
+
+
+def _biased_route(x, w, n, o, k, gated: bool):
+    """Which kernel with a biased read-out takes a bfloat16 product of these sizes: "skinny", "rows", "paired" or None."""
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or _chain_open or decode_products != "skinny" or products == "library":
+        return None
+    if _skinny_fits(n, k):
+        return "skinny"
+    if k % 8 or (gated and o % 16) or (not gated and o % 4):
+        return None
+    if _rows_takes(n, o, k, 2 if gated else 1):
+        return "rows"
+    return "paired" if n > _SKINNY_ROWS else None
+
+
+def _linear_bias(x, w, out_dtype, residual, bias):
+    n, k = x.shape
+    o = w.shape[0]
+    if bias.dtype != torch.float32 or bias.numel() != o or not bias.is_contiguous():
+        raise ValueError("linear: bias must be a dense float32 vector with one number per output channel")
+    route = _biased_route(_dense(x, "x"), _dense(w, "w"), n, o, k, False) if residual is not None and w.shape[1] == k else None
+    if route is None:
+        if residual is not None:
+            return linear(x, w, residual=add_bias(residual, bias))
+        return add_bias(linear(x, w, out_dtype=torch.float32), bias, out_dtype or x.dtype)
+    if residual.dtype != torch.float32 or residual.shape != (n, o) or not residual.is_contiguous():
+        raise ValueError("linear: residual must be contiguous float32 [N, O]")
+    if route == "skinny":
+        _check(_fn("skinny_gemm", "akas_skinny_gemm_more")(_ptr(x), None, None, None, None, _ptr(w), _ptr(residual), n, o, k, 0,
+                                                          _OUT_ACC, _ptr(bias), 0, _stream()), "skinny product with a bias")
+    else:
+        name = "gemm_rows" if route == "rows" else "gemm_pair"
+        _check(_fn(name, f"akas_{name}_bias")(_ptr(x), _ptr(w), _ptr(residual), n, o, k, 1, _ptr(bias), 0, _stream()),
+               f"{name} product with a bias")
+    return residual
+
+
+def linear_gated(x, w_gate_up, width, bias, activation):
+    """act(g + b_g) * (u + b_u) for [g | u] = x . w^T with w the stacked gate and up matrices (``width`` = F rows each,
+    then rows of padding, if any), bias float32 [2F] or None, activation "silu" or "gelu_tanh": [N, F] in x's dtype. In bfloat16 the activation rides in the
+    product's read-out (the [N, 2F] intermediate is never written); elsewhere the product leaves float32 and
+    ``gated_activation`` follows."""
+    n, k = x.shape
+    f2 = w_gate_up.shape[0]
+    if activation not in _ACTIVATIONS:
+        raise ValueError(f"unknown activation {activation!r}")
+    if f2 < 2 * width or (bias is not None and (bias.dtype != torch.float32 or bias.numel() != 2 * width or not bias.is_contiguous())):
+        raise ValueError("linear_gated takes the stacked gate and up matrices and a dense float32 bias [2F]")
+    # (rows of padding below the two matrices: the read-out pairs row f with row F + f of exactly 2F rows)
+    route = _biased_route(_dense(x, "x"), _dense(w_gate_up, "w"), n, f2, k, True) if w_gate_up.shape[1] == k and f2 == 2 * width else None
+    if route is None:
+        if _chain_open:
+            chain_flush()
+        return gated_activation(linear(x, w_gate_up, out_dtype=torch.float32), width, bias, activation, x.dtype)
+    out = torch.empty((n, f2 // 2), dtype=torch.bfloat16, device=x.device)
+    act = _READOUT_ACTIVATIONS[activation]
+    if route == "skinny":
+        _check(_fn("skinny_gemm", "akas_skinny_gemm_more")(_ptr(x), None, None, None, None, _ptr(w_gate_up), _ptr(out), n, f2, k, 0,
+                                                          _OUT_SWIGLU, _ptr(bias), act, _stream()), "skinny gated product")
+    else:
+        name = "gemm_rows" if route == "rows" else "gemm_pair"
+        _check(_fn(name, f"akas_{name}_bias")(_ptr(x), _ptr(w_gate_up), _ptr(out), n, f2, k, 2, _ptr(bias), act, _stream()),
+               f"{name} gated product")
+    return out
+
+
+def dyt_linear(h, alpha, weight, shift, w, out_dtype=None, rows=None, gated=None):
+    """linear(dynamic_tanh(h[rows]), w) for few tokens, the norm computed on the product's way in; with ``gated`` =
+    (width, bias or None, activation) through the gated read-out as ``linear_gated``. None where the fused kernel does not take
+    the sizes or the dtype (the caller then runs the norm by itself)."""
+    m = rows.numel() if rows is not None else h.shape[0]
+    k, o = h.shape[1], w.shape[0]
+    if (w.dtype != torch.bfloat16 or h.dtype != torch.float32 or not h.is_contiguous() or w.shape[1] != k or _chain_open
+            or decode_products != "skinny" or not _skinny_fits(m, k) or alpha.dtype != torch.float32):
+        return None
+    bias, act, mode = None, 0, _OUT_F32 if out_dtype == torch.float32 else _OUT_BF16
+    if gated is not None:
+        width, bias, activation = gated
+        if o != 2 * width or activation not in _ACTIVATIONS or (bias is not None and (bias.dtype != torch.float32 or bias.numel() != o)):
+            return None
+        act, mode = _READOUT_ACTIVATIONS[activation], _OUT_SWIGLU
+    elif out_dtype not in (None, torch.bfloat16, torch.float32):
+        return None
+    out = torch.empty((m, o // 2 if gated is not None else o), dtype=torch.float32 if mode == _OUT_F32 else torch.bfloat16,
+                      device=h.device)
+    _check(_fn("skinny_gemm", "akas_skinny_gemm_more")(_ptr(h), _ptr(rows), _ptr(weight), _ptr(shift), _ptr(alpha), _ptr(_dense(w, "w")),
+                                                      _ptr(out), m, o, k, 2, mode, _ptr(bias), act, _stream()),
+           "skinny product behind a norm without sums")
     return out
 
 
@@ -1441,6 +1538,7 @@ def dynamic_tanh(x, alpha, weight, shift, out_dtype, rows=None):
 
 
 _ACTIVATIONS = {"gelu_tanh": 0, "silu": 1}
+_READOUT_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}  # the products' gated read-outs number them from their first, silu
 
 
 @_flushes

@@ -37,9 +37,12 @@ def rmsnorm(x, weight, eps, zero_centered, out_dtype, rows=None):
     return y.to(out_dtype)
 
 
-def linear(x, w, out_dtype=None, residual=None):
-    """x [N, K] times w [O, K] transposed, float32 accumulation; ``residual`` (float32) is added to in place."""
+def linear(x, w, out_dtype=None, residual=None, bias=None):
+    """x [N, K] times w [O, K] transposed, float32 accumulation, plus ``bias`` (float32 [O]) where one is given, before
+    the one rounding; ``residual`` (float32) is added to in place."""
     y = x.to(torch.float32) @ w.to(torch.float32).T
+    if bias is not None:
+        y = y + bias
     if residual is not None:
         residual += y
         return residual
@@ -533,6 +536,12 @@ def gated_activation(gate_up, width, bias, activation, out_dtype, residual=None,
     if bias is not None:
         g, u = g + bias[:width], u + bias[width:]
     return (_activation(g, activation) * u).to(out_dtype)
+
+
+def linear_gated(x, w_gate_up, width, bias, activation):
+    """act(g + b_g) * (u + b_u) for [g | u | ...] = x . w^T with w the stacked gate and up matrices (``width`` = F rows
+    each, then rows of padding, if any) -> [N, F] in x's dtype."""
+    return gated_activation(linear(x, w_gate_up, out_dtype=torch.float32), width, bias, activation, x.dtype)
 
 
 def latent_norm_store(proj, q_rank, kv_rank, rot, q_weight, kv_weight, eps, cos, sin, interleaved, pool, block_table,

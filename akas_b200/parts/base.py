@@ -150,14 +150,37 @@ class Normed:
         return self._tensor
 
 
-def project(rt: "Runtime", x, w, out_dtype=None, residual=None):
-    """``x . w^T`` for a tensor or a ``Normed``; with ``residual`` the product is added into it."""
+def project(rt: "Runtime", x, w, out_dtype=None, residual=None, bias=None):
+    """``x . w^T`` for a tensor or a ``Normed``; with ``residual`` the product is added into it; ``bias`` (float32, one
+    number per output channel) is added before the result is rounded."""
     if isinstance(x, Normed):
         spec = x.norm.spec
-        if residual is None and getattr(spec, "kind", None) == "rmsnorm" and hasattr(rt.ops, "norm_linear"):
+        kind = getattr(spec, "kind", None)
+        if residual is None and bias is None and kind == "rmsnorm" and hasattr(rt.ops, "norm_linear"):
             return rt.ops.norm_linear(x.h, x.norm.weight, spec.eps, spec.zero_centered, w, out_dtype, x.rows)
+        if residual is None and bias is None and kind == "dynamic_tanh" and hasattr(rt.ops, "dyt_linear"):
+            out = rt.ops.dyt_linear(x.h, x.norm.alpha, x.norm.weight, x.norm.shift, w, out_dtype, x.rows)
+            if out is not None:
+                return out
         x = x.tensor()
+    if bias is not None:
+        return rt.ops.linear(x, w, out_dtype=out_dtype, residual=residual, bias=bias)
     return rt.ops.linear(x, w, out_dtype=out_dtype, residual=residual)
+
+
+def project_gated(rt: "Runtime", x, w_gate_up, width, bias, activation):
+    """``act(x . w_g^T + b_g) * (x . w_u^T + b_u)`` for the stacked ``[w_g; w_u]`` (``width`` rows each), for a tensor or a ``Normed``: in the
+    read-out of the product where the kernels offer that, else the product in float32 and the activation's kernel."""
+    ops = rt.ops
+    if isinstance(x, Normed):
+        if getattr(x.norm.spec, "kind", None) == "dynamic_tanh" and hasattr(ops, "dyt_linear"):
+            out = ops.dyt_linear(x.h, x.norm.alpha, x.norm.weight, x.norm.shift, w_gate_up, None, x.rows, gated=(width, bias, activation))
+            if out is not None:
+                return out
+        x = x.tensor()
+    if hasattr(ops, "linear_gated"):
+        return ops.linear_gated(x, w_gate_up, width, bias, activation)
+    return ops.gated_activation(ops.linear(x, w_gate_up, out_dtype=torch.float32), width, bias, activation, rt.dtype)
 
 
 def project_swiglu(rt: "Runtime", x, w_gate_up):

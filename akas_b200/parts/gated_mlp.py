@@ -1,17 +1,18 @@
 """A gated feed-forward with a choice of activation and optional biases:
 W_down (act(W_gate x + b_gate) * (W_up x + b_up)) + b_down.
 
-W_gate and W_up are stacked at load so that one product feeds the activation. That product leaves float32; the
-biases, the activation and the product of the two halves are float32 (``ops.gated_activation``), rounded once to the
-compute dtype as the down product's operand. The down bias is added to the float32 residual stream by the
-activation's launch; the down product then accumulates into that stream.
+W_gate and W_up are stacked at load so that one product feeds the activation. The biases, the activation and the
+product of the two halves are float32, computed on the product's float32 sums in its read-out (``ops.linear_gated``;
+where the kernels do not offer that, the product leaves float32 and ``ops.gated_activation`` follows) and rounded once
+to the compute dtype as the down product's operand. The down product adds its sums and its bias into the float32
+residual stream.
 """
 
 from __future__ import annotations
 
 import torch
 
-from .base import FeedForward, Param, project, register_ffn, renamed, stack_rows
+from .base import FeedForward, Param, project, project_gated, register_ffn, renamed, stack_rows
 
 ACTIVATIONS = ("gelu_tanh", "silu")
 
@@ -46,17 +47,11 @@ class GatedMLP(FeedForward):
             self.bias_down = get(self._n("down") + ".b")
 
     def forward(self, x, ctx, residual=None):
-        ops = self.rt.ops
-        gate_up = project(self.rt, x, self.w_gate_up, out_dtype=torch.float32)
-        more = {}
-        if residual is not None and self.bias_down is not None:
-            more = dict(residual=residual, residual_bias=self.bias_down)  # the same launch adds the last product's bias
-        act = ops.gated_activation(gate_up, self.spec.intermediate_size, self.bias_gate_up, self.spec.activation, self.rt.dtype,
-                                   **more)
+        act = project_gated(self.rt, x, self.w_gate_up, self.spec.intermediate_size, self.bias_gate_up, self.spec.activation)
         if residual is None:
-            out = project(self.rt, act, self.w_down, out_dtype=torch.float32)
-            return ops.add_bias(out, self.bias_down, self.rt.dtype) if self.bias_down is not None else out.to(self.rt.dtype)
-        return project(self.rt, act, self.w_down, residual=residual)
+            out = project(self.rt, act, self.w_down, out_dtype=torch.float32, bias=self.bias_down)
+            return out.to(self.rt.dtype)
+        return project(self.rt, act, self.w_down, residual=residual, bias=self.bias_down)
 
 
 register_ffn("gated_mlp", GatedMLP)

@@ -739,3 +739,84 @@ def test_attention_over_rows_that_hold_key_and_value(heads, width, vdim, window,
         ctx1 = SimpleNamespace(query_lens=(1, 1, 1, 1), decode_only=True, cu_seqlens=cu1, max_context=most)
         got1 = cuda.attention_general(q1, pool, pool, table, seq1, pos1, *args, ctx1, sinks=sinks, values_in_keys=vdim)
         _close(got1, want1, tol, f"single tokens, keys in parts: {most > 0}")
+
+
+def _plain_gated(x, w2, f, bias, activation):
+    gu = x.double() @ w2.double().T
+    g, u = gu[:, :f], gu[:, f : 2 * f]
+    if bias is not None:
+        g, u = g + bias[:f].double(), u + bias[f:].double()
+    act = g * torch.sigmoid(g) if activation == "silu" else 0.5 * g * (1 + torch.tanh(math.sqrt(2 / math.pi) * (g + 0.044715 * g ** 3)))
+    return act * u
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,k,o", [(3, 64, 48), (16, 192, 320), (9, 2048, 48), (1, 128, 1008), (40, 264, 528), (128, 2048, 320),
+                                   (17, 64, 16), (300, 96, 208), (2048, 256, 512), (333, 520, 1168), (5, 100, 36), (60, 52, 20)])
+def test_products_with_biases_and_a_gated_read_out(n, k, o, dtype):
+    """x . w^T + b rounded once, added into a float32 stream, and act(g + b_g) * (u + b_u) from the stacked gate and up
+    matrices, at sizes for each product kernel (few tokens, up to 128, more) and sizes that none of them takes."""
+    from akas_b200.ops import cuda
+
+    cuda.require()
+    g = torch.Generator().manual_seed(n + k + o)
+    x = torch.randn(n, k, generator=g).to(dtype).cuda()
+    w = (torch.randn(o, k, generator=g) * 0.05).to(dtype).cuda()
+    b = torch.randn(o, generator=g).cuda()
+    tol = 3e-6 * max(1.0, (k / 64) ** 0.5) if dtype == torch.float32 else 1e-2
+    want = x.double() @ w.double().T + b.double()
+    got = cuda.linear(x, w, bias=b)
+    assert got.dtype == dtype
+    _close(got, want, tol, "bias, rounded once")
+    _close(cuda.linear(x, w, out_dtype=torch.float32, bias=b), want, tol, "bias, float32 out")
+    h = (torch.randn(n, o, generator=g) * 2.0).cuda()
+    h0 = h.clone()
+    assert cuda.linear(x, w, residual=h, bias=b) is h
+    _close(h, h0.double() + want, tol, "bias and product into the stream")
+    if o % 2 == 0:
+        f = o // 2
+        for activation in ("gelu_tanh", "silu"):
+            for bias in (b, None):
+                got = cuda.linear_gated(x, w, f, bias, activation)
+                assert got.shape == (n, f) and got.dtype == dtype
+                _close(got, _plain_gated(x, w, f, bias, activation), tol, f"gated {activation} bias {bias is not None}")
+    padded = torch.cat([w, torch.zeros(16, k, dtype=dtype, device="cuda")])  # rows of padding below the two matrices
+    if o % 2 == 0:
+        _close(cuda.linear_gated(x, padded, o // 2, b, "gelu_tanh"), _plain_gated(x, w, o // 2, b, "gelu_tanh"), tol, "padded")
+    assert cuda.skinny_status() == 0 and cuda.gemm_rows_status() == 0 and cuda.gemm_pair_status() == 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("m,k,o", [(1, 64, 48), (8, 192, 320), (9, 2048, 48), (16, 1024, 1008), (5, 128, 16), (3, 100, 40), (20, 64, 32)])
+def test_a_norm_without_sums_in_front_of_a_product(m, k, o):
+    """tanh(alpha x) * w + b of gathered float32 rows as the way into a product of few tokens, with the plain, the
+    float32 and the gated read-out; sizes the kernel does not take are refused with None."""
+    from akas_b200.ops import cuda
+
+    cuda.require()
+    g = torch.Generator().manual_seed(m + k + o)
+    h = (torch.randn(m + 3, k, generator=g) * 3.0).cuda()
+    alpha = torch.tensor(0.6).cuda()
+    nw, nb = torch.randn(k, generator=g).cuda(), (torch.randn(k, generator=g) * 0.3).cuda()
+    w = (torch.randn(o, k, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    bias = torch.randn(o, generator=g).cuda()
+    rows = torch.randperm(m + 3, generator=g)[:m].to(torch.int32).cuda()
+    for r in (None, rows):
+        src = h[:m] if r is None else h[r.long()]
+        normed = (torch.tanh(alpha.double() * src.double()) * nw.double() + nb.double()).to(torch.bfloat16)
+        want = normed.double() @ w.double().T
+        got = cuda.dyt_linear(h[:m].contiguous() if r is None else h, alpha, nw, nb, w, None, r)
+        if k % 64 or m > 16:
+            assert got is None
+            return
+        assert got.dtype == torch.bfloat16
+        _close(got, want, 1e-2, "rounded out")
+        got = cuda.dyt_linear(h[:m].contiguous() if r is None else h, alpha, nw, nb, w, torch.float32, r)
+        assert got.dtype == torch.float32
+        _close(got, want, 2e-3, "float32 out")
+        for activation in ("gelu_tanh", "silu"):
+            for b in (bias, None):
+                got = cuda.dyt_linear(h[:m].contiguous() if r is None else h, alpha, nw, nb, w, None, r, gated=(o // 2, b, activation))
+                _close(got, _plain_gated(normed, w, o // 2, b, activation), 1e-2, f"gated {activation} bias {b is not None}")
+    assert cuda.skinny_status() == 0
