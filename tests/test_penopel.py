@@ -611,14 +611,17 @@ def test_latent_norm_store_kernel(q_rank, kv_rank, rot, interleaved, page, dtype
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,o,k,t", [(4, 32, 24, 8), (20, 48, 8, 16), (3, 18, 20, 6), (5, 24, 16, 0), (2, 300, 72, 0), (3, 40, 520, 4),
-                                         (16, 64, 512, 0), (1, 7, 5, 2)])
-def test_head_linear_kernel(heads, o, k, t, dtype):
+@pytest.mark.parametrize("heads,o,k,t,n", [(4, 32, 24, 8, 37), (20, 48, 8, 16, 37), (3, 18, 20, 6, 37), (5, 24, 16, 0, 37),
+                                           (2, 300, 72, 0, 37), (3, 40, 520, 4, 37), (16, 64, 512, 0, 37), (1, 7, 5, 2, 37),
+                                           (6, 96, 64, 32, 150), (6, 64, 96, 0, 21), (3, 32, 16, 8, 64), (2, 512, 128, 64, 200),
+                                           (40, 48, 160, 0, 2100), (5, 16, 32, 6, 70)])
+def test_head_linear_kernel(heads, o, k, t, n, dtype):
+    """Sizes for the plain kernel and (inner and outer sizes that are multiples of 16, in bfloat16) for the one on the
+    tensor cores: a part of a tile, several tiles, more tiles than a block's share."""
     from akas_b200.ops import cuda, reference
 
     cuda.require(["latent", "rope"])
     g = torch.Generator().manual_seed(heads + o + k)
-    n = 37
     wide = torch.randn(n, heads * (k + t) + 8, generator=g).to(dtype).cuda()
     x = wide[:, : heads * (k + t)]
     w = (torch.randn(heads, o, k, generator=g) / k ** 0.5).to(dtype).cuda()
