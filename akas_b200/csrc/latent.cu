@@ -28,20 +28,23 @@ latent_norm_store_kernel(const float* __restrict__ proj, long long ld, int QR, i
   const int n = blockIdx.x;
   const int req = seq_of_token[n];
   if (req < 0) return;
+  // everything the block reads is asked for before the first sum meets: the token's place, its page, both latents
+  const int pos = positions[n];
   const float* row = proj + (size_t)n * ld;
-  float ss = 0.f;
+  const float* c = row + QR;
+  float ss = 0.f, sc = 0.f;
   for (int i = threadIdx.x; i < QR; i += blockDim.x) { const float x = row[i]; ss = fmaf(x, x, ss); }
+  int page = 0;
+  if (write) {
+    for (int i = threadIdx.x; i < KR; i += blockDim.x) { const float x = c[i]; sc = fmaf(x, x, sc); }
+    page = block_table[(size_t)req * max_blocks + pos / page_size];
+  }
   ss = block_sum(ss, scratch);
+  if (write) sc = block_sum(sc, scratch);  // (`write` is the same for the whole launch)
   const float inv_q = 1.f / sqrtf(ss / (float)QR + eps);
   for (int i = threadIdx.x; i < QR; i += blockDim.x) q_out[(size_t)n * QR + i] = from_f32<T>(row[i] * inv_q * qw[i]);
   if (!write) return;
-  const float* c = row + QR;
-  float sc = 0.f;
-  for (int i = threadIdx.x; i < KR; i += blockDim.x) { const float x = c[i]; sc = fmaf(x, x, sc); }
-  sc = block_sum(sc, scratch);
   const float inv_c = 1.f / sqrtf(sc / (float)KR + eps);
-  const int pos = positions[n];
-  const int page = block_table[(size_t)req * max_blocks + pos / page_size];
   T* dst = pool + ((size_t)page * page_size + pos % page_size) * (size_t)(KR + rot);
   for (int i = threadIdx.x; i < KR; i += blockDim.x) dst[i] = from_f32<T>(c[i] * inv_c * kw[i]);
   const float* tail = c + KR;

@@ -80,3 +80,28 @@ def test_generate_runs_a_girelix_folder(tmp_path, capsys):
     for extra in ([], ["--temperature", "0.7", "--top-k", "20", "--seed", "2", "--dtype", "float32"]):
         main(["generate", "--model", str(tmp_path / "g"), "--prompt", "5 17 3 9", "--max-tokens", "7", "--ignore-eos", *extra])
         assert len(capsys.readouterr().out.split()) == 7
+
+
+def test_random_and_inspect_take_a_penopel_configuration(tmp_path, capsys):
+    import tiny_penopel
+
+    config = tiny_penopel.CONFIGS["mix"]
+    main(["random", "--out", str(tmp_path / "p"), "--config", json.dumps(config), "--seed", "4"])
+    capsys.readouterr()
+    main(["inspect", "--model", str(tmp_path / "p")])
+    report = json.loads(capsys.readouterr().out)
+    assert report["architecture"] == "Penopel" and report["config"] == json.loads(json.dumps(config))
+    assert {"l0.norm1.alpha", "l0.mix.dkv.norm", "l0.mix.sink", "l1.mix.k.b", "l1.mlp.down.b", "l3.mix.q.b", "final.norm.b",
+            "head"} <= set(report["inventory"])
+    assert "l3.mix.k" not in report["inventory"]  # the layer reads another layer's keys and values
+
+
+@pytest.mark.gpu
+def test_generate_runs_a_penopel_folder(tmp_path, capsys):
+    import tiny_penopel
+
+    main(["random", "--out", str(tmp_path / "p"), "--config", json.dumps(tiny_penopel.CONFIGS["mix"]), "--seed", "4"])
+    capsys.readouterr()
+    for extra in ([], ["--temperature", "0.7", "--top-k", "20", "--seed", "2", "--dtype", "float32"]):
+        main(["generate", "--model", str(tmp_path / "p"), "--prompt", "5 17 3 9", "--max-tokens", "7", "--ignore-eos", *extra])
+        assert len(capsys.readouterr().out.split()) == 7
