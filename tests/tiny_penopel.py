@@ -28,6 +28,12 @@ LAT_ODD = dict(heads=3, dim=20, rot_dim=6, vdim=12, q_rank=28, kv_rank=18, scale
                rot=dict(base=1000000.0, dims=6))
 LAT_SELF = dict(heads=2, dim=12, rot_dim=4, vdim=20, q_rank=10, kv_rank=14, scale=0.5, mask=dict(size=1),
                 rot=dict(base=50.0, dims=4))
+ATT_BIG = dict(heads=4, kv_heads=1, dim=128, vdim=128, scale=0.09, rot=dict(base=500000.0, dims=128))
+ATT_MID = dict(heads=8, kv_heads=4, dim=64, vdim=32, scale=0.125, rot=dict(base=10000.0, dims=32, scaling=SLOWED))
+LAT_ROW64 = dict(heads=12, dim=48, rot_dim=16, vdim=16, q_rank=128, kv_rank=48, scale=0.15, mask=dict(size=64),
+                 rot=dict(base=1000000.0, dims=16))
+LAT_ROW320 = dict(heads=2, dim=128, rot_dim=64, vdim=128, q_rank=32, kv_rank=256, scale=0.07, mask=dict(size=33),
+                  rot=dict(base=100.0, dims=64))
 LAT_OPEN = dict(heads=5, dim=16, rot_dim=0, vdim=8, q_rank=16, kv_rank=24, scale=0.35, rot=dict(base=10.0, dims=0))  # no mask, no rotation
 
 
@@ -65,9 +71,14 @@ CONFIGS = {
     # sizes that are multiples of nothing much: rows of 50 and 77
     "ragged": model(50, 77, [att(ATT_BARE, 10), lat(LAT_ODD, 14), att(ATT_BARE, None, kv_from=0)], eps=1e-3, scale=-2.2, cap=5.0),
     "latent": model(48, 120, [lat(LAT, None), lat(LAT_WIDE, 24)], scale=4.0),
+    # sizes that the tensor-core kernels take (heads of 128 and 64 with values of 128 and 32, cached rows of 64) beside a
+    # cached row of 320 numbers that they do not; windows of a page, of half a page and none
+    "mid": model(128, 300, [att(ATT_BIG, 192), lat(LAT_ROW64, 192), lat(LAT_ROW320, 192), att(ATT_MID, 192)], eps=1e-6, scale=11.3,
+                 cap=None),
 }
-PAGE = {"mix": 8, "odd": 16, "ragged": 32, "latent": 64}
-LENGTHS = {"mix": [1, 45, 2, 97, 33, 130, 64], "odd": [70, 3, 41, 100], "ragged": [75, 2, 140], "latent": [90, 1, 150]}
+PAGE = {"mix": 8, "odd": 16, "ragged": 32, "latent": 64, "mid": 64}
+LENGTHS = {"mix": [1, 45, 2, 97, 33, 130, 64], "odd": [70, 3, 41, 100], "ragged": [75, 2, 140], "latent": [90, 1, 150],
+           "mid": [200, 129, 64]}
 TOL = {"float32": 3e-5, "bfloat16": 3e-2}  # largest |difference| over largest |reference logit|
 
 
