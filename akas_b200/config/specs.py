@@ -60,6 +60,14 @@ class RopeSpec:
     # l < original / high, turns at f / factor where l > original / low, and in between at (1 - s) f / factor + s f with
     # s = (original / l - low) / (high - low). None: every pair keeps its rate.
     scaling: Optional[Tuple[float, float, float, float]] = None
+    # Every pair's rate divided by this number (positions stretched evenly). None: rates as they are.
+    linear_factor: Optional[float] = None
+    # Rates blended by the pair's index, as (factor, original, fast, slow): with
+    # d(t) = rotary * ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(d(fast)), 0),
+    # hi = min(ceil(d(slow)), rotary - 1) and r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns at
+    # r_i f_i / factor + (1 - r_i) f_i.
+    blend: Optional[Tuple[float, float, float, float]] = None
+    amplitude: float = 1.0  # cosine and sine are both multiplied by this number
 
     @property
     def rotary(self) -> int:
@@ -88,7 +96,9 @@ class AttentionSpec:
     # one more term in the softmax's denominator, without a key or a value: True: exp(0); "learned": exp(sink_h) with
     # a tensor [heads] of logits, which the scale does not touch
     sink: Any = False
-    gate: Optional[str] = None  # "head": head h's output times sigmoid(W_g x)_h, W_g [heads, hidden], x the mixer's input
+    # "head": head h's output times sigmoid(W_g x)_h, W_g [heads, hidden], x the mixer's input; "channel": the
+    # concatenated heads times sigmoid(W_g x) element by element, W_g [heads * value_dim, hidden]
+    gate: Optional[str] = None
     # The values are the keys as projected (before QK-norm and the position encoding): there is no value matrix, and
     # the value heads have the keys' size.
     values_are_keys: bool = False
@@ -119,14 +129,16 @@ class LatentAttentionSpec:
     are a key part that all heads share. Per head the plain key is W_uk c and the value W_uv c;
     score = (q_plain . k_plain + q_rot . k_rot) * scale. ``window``: position i sees j with 0 <= i - j < window
     (None: every earlier key). ``sink``: as for ``AttentionSpec``. ``gate="channel"``: the concatenated heads times
-    sigmoid(W_g x), element by element, before the output product."""
+    sigmoid(W_g x), element by element, before the output product; ``gate="head"``: head h's output times
+    sigmoid(W_g x)_h with W_g [heads, hidden]. ``q_rank`` None: the queries are one projection of the input,
+    q = W_q x (a tensor ``q``), with no latent and no norm of their own."""
 
     hidden_size: int
     num_heads: int
     head_dim: int
     rope_dim: int
     v_head_dim: int
-    q_rank: int
+    q_rank: Optional[int]
     kv_rank: int
     norm_eps: float
     scale: float
@@ -174,6 +186,17 @@ class GatedMLPSpec:
 
 
 @dataclass(frozen=True)
+class MLPSpec:
+    """W_down act(W_up x) without a gate; ``activation`` one of "relu2" (the square of max(z, 0)), "gelu_tanh", "silu"."""
+
+    hidden_size: int
+    intermediate_size: int
+    activation: str = "relu2"
+    kind: str = "mlp"
+    names: Mapping[str, str] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
 class GatedLinearAttentionSpec:
     """Linear attention with a decay per key channel: S <- diag(alpha) S + k v^T, o = S^T q, per head.
 
@@ -198,8 +221,9 @@ class DecayedLinearAttentionSpec:
 
     q, k [heads x key_dim] and v [heads x value_dim] pass ``activation`` ("silu" or None) after their products. The
     read-out is RMS-normed, over all heads together when ``whole_norm`` (weight [heads * value_dim]), else per head
-    (weight [value_dim] shared by the heads), and multiplied by ``gate_activation`` ("sigmoid" or "silu") of W_g x
-    before the output product. The state is float32 and starts at zero."""
+    (weight [value_dim] shared by the heads; ``norm_weight`` False: the division alone, no tensor), and multiplied by
+    ``gate_activation`` ("sigmoid" or "silu") of W_g x before the output product. The state is float32 and starts at
+    zero."""
 
     hidden_size: int
     num_heads: int
@@ -211,6 +235,7 @@ class DecayedLinearAttentionSpec:
     whole_norm: bool = True
     gate_activation: str = "sigmoid"
     q_scale: float = 1.0
+    norm_weight: bool = True
     kind: str = "decayed_linear_attention"
     names: Mapping[str, str] = field(default_factory=dict)
 
@@ -235,7 +260,14 @@ class RoutedExpertsSpec:
     The router has ``num_experts + num_identity`` outputs; the last ``num_identity`` are experts without tensors
     that return their input. Scores are a softmax over all outputs (float32); the choice goes by score plus a
     learned correction, among the outputs of the ``keep_groups`` best of ``groups`` equal groups of neighbours (a
-    group's score is its largest choice score); the weights are the chosen outputs' plain scores over their sum."""
+    group's score is its largest choice score); the weights are the chosen outputs' plain scores over their sum.
+
+    Options: ``scoring="sigmoid"``: every output's score is the sigmoid of its logit; ``correction`` False: no
+    correction tensor, the choice goes by the plain scores; ``renormalize`` False: the weights are the chosen
+    scores as they are; ``weight_on="input"``: the weight multiplies the expert's input, the result is
+    sum expert(w x), where otherwise it is sum w expert(x); ``shared_size`` F_s: one more expert of that hidden size
+    (tensors ``shared.{gate,up,down}``) that every token passes, added to the sum, and with ``shared_gate`` times
+    sigmoid(W_sg x), one number per token (``shared.sg`` [1, hidden])."""
 
     hidden_size: int
     intermediate_size: int
@@ -244,6 +276,12 @@ class RoutedExpertsSpec:
     top: int
     groups: int = 1
     keep_groups: int = 1
+    scoring: str = "softmax"
+    correction: bool = True
+    renormalize: bool = True
+    weight_on: str = "output"
+    shared_size: Optional[int] = None
+    shared_gate: bool = False
     kind: str = "routed_experts"
     names: Mapping[str, str] = field(default_factory=dict)
 
@@ -299,6 +337,12 @@ class LayerSpec:
     mixer_norm_name: str
     ffn_norm_name: Optional[str]
     arrangement: str = "pre_norm"
+    # What the "sandwich" arrangement adds: a second norm behind each sublayer, on its result, before the sum:
+    # h += mixer_post_norm(mixer(mixer_norm(h))); h += ffn_post_norm(ffn(ffn_norm(h))).
+    mixer_post_norm: Any = None
+    ffn_post_norm: Any = None
+    mixer_post_norm_name: Optional[str] = None
+    ffn_post_norm_name: Optional[str] = None
     # What the "parallel" arrangement adds: h += residual_multiplier * (mixer_scale * mixer(n) + ffn_scale * ffn(n))
     # with ONE norm n = mixer_norm(h) that both sublayers read; the two scales are tensors [hidden] (None: ones).
     residual_multiplier: float = 1.0
@@ -314,11 +358,13 @@ class ScheduleEntry:
     default an entry owns its own cache. An entry whose ``cache`` is another
     entry's index reads that entry's cache and writes nothing into it (the mixer
     is told ``write=False``). Naming a layer in two entries runs its weights twice,
-    each time with the cache of its own entry.
+    each time with the cache of its own entry. ``add_embedding``: before the layer runs, the embedding's output (the
+    stream as it was in front of the first entry) is added to the stream once more.
     """
 
     layer: int
     cache: Optional[int] = None
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)

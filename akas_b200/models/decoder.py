@@ -2,8 +2,8 @@
 
 Embedding (times ``ModelSpec.embedding_multiplier`` if the architecture has one, plus a learned position vector
 and through a norm if it has those), the blocks of
-``ModelSpec.layers`` in the order of ``ModelSpec.schedule`` (a list that may name a layer twice or let an
-entry read another entry's cache), the final norm on the rows whose logits are wanted, the head, and the
+``ModelSpec.layers`` in the order of ``ModelSpec.schedule`` (a list that may name a layer twice, let an
+entry read another entry's cache, or have the embedding's output added again in front of an entry), the final norm on the rows whose logits are wanted, the head, and the
 architecture's ``logit_scale`` and ``logit_softcap`` if it has them. The head is the checkpoint's
 head tensor when it has one, else the embedding:
 src/akas/models/lfm2/weights.py:399-402 and _composition.py:363-380 in kreasof-ai/akas).
@@ -103,11 +103,19 @@ class Decoder:
             h = ops.add_rows(h, self.positions, ctx.positions)
         if self.embedding_norm is not None:
             h = self.embedding_norm.forward(h, out_dtype=torch.float32)  # the residual stream stays float32
+        # entries that add the embedding's output again read a copy of it (the blocks add into h in place)
+        first = None
+        if any(entry.add_embedding for entry in self.schedule):
+            if chained:
+                ops.chain_flush()
+            first = h.clone()
         for i, entry in enumerate(self.schedule):
             owner = i if entry.cache is None else entry.cache
             block = self.blocks[entry.layer]
             if chained and not block.chain_safe:
                 ops.chain_flush()
+            if entry.add_embedding:
+                h = ops.scaled_add(h, first, None, None, None, 1.0)
             h = block.forward(h, ctx, caches[owner], write=entry.cache is None)
         if chained and not getattr(self.final_norm, "chain_safe", False):
             ops.chain_flush()

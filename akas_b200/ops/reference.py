@@ -105,9 +105,10 @@ def scale_cap(x, scale=1.0, cap=0.0):
     return x
 
 
-def rope_tables(positions, inv_freq):
+def rope_tables(positions, inv_freq, amplitude=1.0):
+    """cos and sin of position x rate, both times ``amplitude``, float32 [N, pairs]."""
     ang = positions.to(torch.float64)[:, None] * inv_freq[None, :]
-    return torch.cos(ang).to(torch.float32), torch.sin(ang).to(torch.float32)
+    return (amplitude * torch.cos(ang)).to(torch.float32), (amplitude * torch.sin(ang)).to(torch.float32)
 
 
 def _page_addresses(block_table, seq_of_token, positions, page_size):
@@ -381,13 +382,15 @@ def delta_scan(q, k, v, beta, g, state, cu_seqlens, slots, heads, kv_heads, dim,
 
 
 def gated_rmsnorm(o, weight, eps, gate, heads, vdim, out_dtype, gate_activation="silu", out=None, out_scale=1.0):
-    """Each head of o [N, heads * vdim] over its root mean square (eps under the root), times weight [vdim], times
+    """Each head of o [N, heads * vdim] over its root mean square (eps under the root), times weight [vdim] (None: ones), times
     silu(gate) [N, heads * vdim] (or, ``gate_activation="sigmoid"``, sigmoid(gate)), times ``out_scale``; written into
     ``out`` (a view [N, heads * vdim] whose rows may be parts of wider rows) where that is given. A norm over all
     heads together is the call with heads = 1."""
     n = o.shape[0]
     of = o.to(torch.float64).reshape(n, heads, vdim)
-    of = of / torch.sqrt((of * of).mean(dim=-1, keepdim=True) + eps) * weight.to(torch.float64)
+    of = of / torch.sqrt((of * of).mean(dim=-1, keepdim=True) + eps)
+    if weight is not None:
+        of = of * weight.to(torch.float64)
     gf = gate.to(torch.float64)
     act = torch.sigmoid(gf) if gate_activation == "sigmoid" else gf * torch.sigmoid(gf)
     y = of.reshape(n, heads * vdim) * act * out_scale
@@ -451,8 +454,10 @@ def qk_norm_store(q, k, v, heads, kv_heads, dim, vdim, q_weight, k_weight, eps, 
 
 
 def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, scale, window, keep_first, softcap,
-                      r1, r2, sink, gate, page_size, ctx=None, sinks=None, out=None, out_scale=1.0, values_in_keys=0):
+                      r1, r2, sink, gate, page_size, ctx=None, sinks=None, out=None, out_scale=1.0, values_in_keys=0,
+                      gate_channels=False):
     """``values_in_keys`` = V > 0: a key's row holds its value too, as its first V channels (``v_pool`` is not read).
+    ``gate_channels``: ``gate`` is [N, heads * vdim], one logit per channel of the output, not one per head.
     Attention of every token over the keys of its request that it sees: j <= i and (no window, or i - j < window,
     or j < keep_first). score = q . k * scale; with softcap, cap * tanh(score / cap); with r1 and r2 (float32
     [heads]), minus r1_h * ln(1 + r2_h * (i - j)); softmax over the keys, with ``sink`` one more term exp(0) in the
@@ -497,7 +502,9 @@ def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, s
         e = torch.exp(s - top)
         denom = e.sum(dim=-1, keepdim=True) + (torch.exp(level - top) if level is not None else 0.0)
         out[t] = torch.einsum("kgs,skd->kgd", e / denom, vals).reshape(heads, vd)
-    if gate is not None:
+    if gate is not None and gate_channels:
+        out = out * torch.sigmoid(gate.to(torch.float64)).reshape(n, heads, vd)
+    elif gate is not None:
         out = out * torch.sigmoid(gate.to(torch.float64))[:, :, None]
     result = (out * out_scale).reshape(n, heads * vd)
     if given is not None:
@@ -509,12 +516,16 @@ def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, s
 # --------------------------------------------------------------------------- latent attention, norms without sums
 
 
-def dynamic_tanh(x, alpha, weight, shift, out_dtype, rows=None):
+def dynamic_tanh(x, alpha, weight, shift, out_dtype, rows=None, residual=None):
     """tanh(alpha * x) * weight + shift per element of float32 x [N, C] (alpha a float32 tensor of one number, weight
-    and shift float32 [C]); ``rows``: int32 indices of the rows to norm and return."""
+    and shift float32 [C]); ``rows``: int32 indices of the rows to norm and return. With ``residual`` (float32 [N, C])
+    the result is added to it in place and it is returned."""
     if rows is not None:
         x = x[rows.long()]
     y = torch.tanh(alpha.to(torch.float32) * x.to(torch.float32)) * weight + shift
+    if residual is not None:
+        residual += y
+        return residual
     return y.to(out_dtype)
 
 
@@ -523,7 +534,14 @@ def _activation(z, kind):
         return 0.5 * z * (1.0 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z * z * z)))
     if kind == "silu":
         return z * torch.sigmoid(z)
+    if kind == "relu2":
+        return torch.relu(z) ** 2
     raise ValueError(f"unknown activation {kind!r}")
+
+
+def activation(z, kind, out_dtype):
+    """act(z) element by element in float32, rounded once to ``out_dtype``; "relu2" is the square of max(z, 0)."""
+    return _activation(z.to(torch.float32), kind).to(out_dtype)
 
 
 def gated_activation(gate_up, width, bias, activation, out_dtype, residual=None, residual_bias=None):
@@ -553,7 +571,10 @@ def latent_norm_store(proj, q_rank, kv_rank, rot, q_weight, kv_weight, eps, cos,
     token's row [kv_rank + rot] of ``pool`` [pages, 1, page, kv_rank + rot]."""
     n = proj.shape[0]
     pf = proj.to(torch.float32)
-    out = rmsnorm(pf[:, :q_rank], q_weight, eps, False, pool.dtype)
+    if q_rank:
+        out = rmsnorm(pf[:, :q_rank], q_weight, eps, False, pool.dtype)
+    else:  # no query latent: only the cached row is made
+        out = torch.empty((n, 0), dtype=pool.dtype, device=proj.device)
     if write:
         c = rmsnorm(pf[:, q_rank : q_rank + kv_rank], kv_weight, eps, False, torch.float32)
         tail = pf[:, q_rank + kv_rank : q_rank + kv_rank + rot]
@@ -602,16 +623,20 @@ def head_linear(x, w, heads, gate=None, cos=None, sin=None, interleaved=False):
 # --------------------------------------------------------------------------- routed experts, parallel blocks
 
 
-def moe_route(h, w_router, correction, groups, keep, top):
+def moe_route(h, w_router, correction, groups, keep, top, scoring="softmax", renormalize=True, extra=0):
     """For every row of h [N, C]: scores = softmax(h . w_router^T) over the R router outputs (float32 w_router
     [R, C]); choice scores = scores + correction [R]; the outputs form ``groups`` equal groups of neighbours whose
     score is their largest choice score, and only outputs of the ``keep`` best groups can be chosen; the ``top``
     largest choice scores win (ties: the lower index). Returns (chosen int32 [N, top], weights float32 [N, top]): the
-    chosen outputs in the order of their choice scores and their plain scores over their sum (+ 1e-20)."""
+    chosen outputs in the order of their choice scores and their plain scores over their sum (+ 1e-20).
+    ``scoring="sigmoid"``: a score is the sigmoid of its logit; ``correction`` None: none; ``renormalize`` False: the
+    weights are the chosen scores as they are. ``extra`` = X > 0: w_router has X more rows [R + X, C] that take no part
+    in the choice; the sigmoids of their logits are returned as a third result, float32 [N, X]."""
     n = h.shape[0]
-    r = w_router.shape[0]
-    s = torch.softmax(h.to(torch.float32) @ w_router.to(torch.float32).T, dim=-1)
-    pick = s + correction.to(torch.float32)
+    r = w_router.shape[0] - extra
+    z = h.to(torch.float32) @ w_router.to(torch.float32).T
+    s = torch.softmax(z[:, :r], dim=-1) if scoring == "softmax" else torch.sigmoid(z[:, :r])
+    pick = s + correction.to(torch.float32) if correction is not None else s
     if groups > 1 and keep < groups:
         best = pick.reshape(n, groups, r // groups).max(dim=-1).values
         order = torch.argsort(best, dim=-1, descending=True, stable=True)
@@ -620,12 +645,17 @@ def moe_route(h, w_router, correction, groups, keep, top):
         pick = pick.masked_fill(~stays.repeat_interleave(r // groups, dim=1), float("-inf"))
     chosen = torch.argsort(pick, dim=-1, descending=True, stable=True)[:, :top]
     w = torch.gather(s, 1, chosen)
-    w = w / (w.sum(dim=-1, keepdim=True) + 1e-20)
+    if renormalize:
+        w = w / (w.sum(dim=-1, keepdim=True) + 1e-20)
+    if extra:
+        return chosen.to(torch.int32), w, torch.sigmoid(z[:, r:]).contiguous()
     return chosen.to(torch.int32), w
 
 
-def moe_experts(h, w_gate_up, w_down, chosen, weights, update=None):
-    """With ``update`` = (x, a, scale_a, scale_b, mult): x += mult * (scale_a * a + scale_b * out) in place, returns x. Else
+def moe_experts(h, w_gate_up, w_down, chosen, weights, update=None, weight_input=False, shared=None):
+    """``weight_input``: the weight multiplies the expert's input, out[n] = sum_k expert(weights[n, k] h[n]) (computed
+    as silu(w g) * (w u) on the float32 sums g, u of the unweighted row). ``shared`` = (y float32 [N, C], gate float32
+    [N, 1] or None): y, times its gate, is added to the sum. With ``update`` = (x, a, scale_a, scale_b, mult): x += mult * (scale_a * a + scale_b * out) in place, returns x. Else
     out[n] = sum_k weights[n, k] * expert_(chosen[n, k])(h[n]) in float32 [N, C]. Expert e < E computes
     w_down[e] (silu(gate) * up) with [gate; up] = w_gate_up[e] h (w_gate_up [E, 2 F, C], w_down [E, C, F]; the hidden
     activations are rounded to h's dtype, as the kernels round them); an expert number from E on returns h itself."""
@@ -641,8 +671,13 @@ def moe_experts(h, w_gate_up, w_down, chosen, weights, update=None):
                 out[rows] += g * hf[rows]
                 continue
             gu = hf[rows] @ w_gate_up[e].to(torch.float32).T
+            if weight_input:
+                gu, g = gu * g, 1.0
             act = (torch.nn.functional.silu(gu[:, : f2 // 2]) * gu[:, f2 // 2 :]).to(h.dtype).to(torch.float32)
             out[rows] += g * (act @ w_down[e].to(torch.float32).T)
+    if shared is not None:
+        y, gate = shared
+        out += y if gate is None else gate.reshape(n, 1) * y
     if update is not None:
         x, a, scale_a, scale_b, mult = update
         return scaled_add(x, a, scale_a, out, scale_b, mult)

@@ -29,6 +29,7 @@ class Attention(Mixer):
     takes_normed = True
     chain_safe = True
     shares_cache = True
+    takes_out_dtype = True
 
     @classmethod
     def kernels(cls, spec):
@@ -48,8 +49,8 @@ class Attention(Mixer):
             raise ValueError(f"unknown sink {s.sink!r}; known: False, True, 'learned'")
         if getattr(s, "values_are_keys", False) and s.value_dim != s.head_dim:
             raise ValueError(f"values that are the keys have the keys' size: {s.value_dim} is not {s.head_dim}")
-        if self.general and getattr(s, "gate", None) not in (None, "head"):
-            raise ValueError(f"unknown output gate {s.gate!r}; known: 'head'")
+        if self.general and getattr(s, "gate", None) not in (None, "head", "channel"):
+            raise ValueError(f"unknown output gate {s.gate!r}; known: 'head', 'channel'")
         if self.general and s.keep_first and not s.window:
             raise ValueError("keep_first needs a window")
         self.own_kv = bool(getattr(s, "own_kv", True))
@@ -68,6 +69,11 @@ class Attention(Mixer):
 
     def _n(self, local):
         return renamed(self.spec, local)
+
+    def _gate_rows(self) -> int:
+        """How many logits the output gate has per token: one per head, or one per channel of the concatenated heads."""
+        s = self.spec
+        return {None: 0, "head": s.num_heads, "channel": s.num_heads * s.value_dim}[s.gate]
 
     def params(self):
         s = self.spec
@@ -89,8 +95,8 @@ class Attention(Mixer):
                     p[self._n(local) + ".b"] = Param((p[self._n(local)].shape[0],), role="vector")
         if self.general and s.sink == "learned":
             p[self._n("sink")] = Param((s.num_heads,), role="vector")
-        if self.general and s.gate == "head":
-            p[self._n("gate.weight")] = Param((s.num_heads, s.hidden_size))
+        if self.general and s.gate is not None:
+            p[self._n("gate.weight")] = Param((self._gate_rows(), s.hidden_size))
         if self.general and s.distance_bias:
             p[self._n("r1")] = Param((s.num_heads,), role="vector")
             p[self._n("r2")] = Param((s.num_heads,), role="vector", mean=0.5)
@@ -108,7 +114,7 @@ class Attention(Mixer):
                 if not self.spec.values_are_keys:
                     names.append(self._n("v_proj.weight"))
             parts = [get(name) for name in names]
-            if self.spec.gate == "head":
+            if self.spec.gate is not None:
                 parts.append(get(self._n("gate.weight")))
             self.w_qkv = stack_rows(parts)
             if self.biased:
@@ -155,7 +161,7 @@ class Attention(Mixer):
         q = proj[:, :nq]
         k = proj[:, nq : nq + nk] if self.own_kv else q  # (with nothing to write, k and v are not read)
         v = k if s.values_are_keys or not self.own_kv else proj[:, nq + nk : nq + nk + nv]
-        gate = proj[:, nq + nk + nv : nq + nk + nv + s.num_heads] if s.gate == "head" else None
+        gate = proj[:, nq + nk + nv : nq + nk + nv + self._gate_rows()] if s.gate is not None else None
         norm = self.q_norm.spec if self.q_norm is not None else None
         if norm is not None and norm.zero_centered:
             raise ValueError("the general attention kernels take a plain QK-norm weight")
@@ -179,21 +185,27 @@ class Attention(Mixer):
             more["out"] = out
         if out_scale != 1.0:
             more["out_scale"] = out_scale
+        if s.gate == "channel":
+            more["gate_channels"] = True
+        if gate is not None and gate.dtype != qn.dtype:
+            gate = gate.to(qn.dtype)  # (a float32 product, because of biases: the gate's logits in the pages' dtype)
         return ops.attention_general(
             qn, cache.k, cache.v, table, ctx.seq_of_token, ctx.positions, self.scale, s.window, s.keep_first,
             s.softcap, self.r1, self.r2, s.sink is True, gate, cache.page_size, ctx, **more,
         )
 
-    def _forward_general(self, x, ctx, cache, residual, write):
+    def _forward_general(self, x, ctx, cache, residual, write, out_dtype=None):
         # with biases the product leaves float32, so that product plus bias is rounded once (by the kernel that adds it)
         proj = project(self.rt, x, self.w_qkv, out_dtype=torch.float32 if self.bias is not None else None)
         out = self.core(proj, ctx, cache, write)
-        return project(self.rt, out, self.w_out, residual=residual)
+        return project(self.rt, out, self.w_out, out_dtype=out_dtype, residual=residual)
 
-    def forward(self, x, ctx, cache=None, residual=None, write=True):
+    def forward(self, x, ctx, cache=None, residual=None, write=True, out_dtype=None):
         s, ops = self.spec, self.rt.ops
         if self.general:
-            return self._forward_general(x, ctx, cache, residual, write)
+            return self._forward_general(x, ctx, cache, residual, write, out_dtype)
+        if out_dtype is not None and residual is None:
+            return self.forward(x, ctx, cache, None, write).to(out_dtype)
         qkv = project(self.rt, x, self.w_qkv)
         fused = self.position is None or hasattr(self.position, "tables")
         cos = sin = None

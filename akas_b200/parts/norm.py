@@ -63,6 +63,11 @@ class DynamicTanh(Part):
     def lazy(self, h, rows=None) -> Normed:
         return Normed(self, h, rows)
 
+    def add_to(self, y, h):
+        """h += norm(y) in place on the float32 stream h [N, size], for float32 y: the norm behind a sublayer and the
+        residual sum as one kernel."""
+        return self.rt.ops.dynamic_tanh(y, self.alpha, self.weight, self.shift, torch.float32, residual=h)
+
 
 register_norm("rmsnorm", RMSNorm)
 register_norm("dynamic_tanh", DynamicTanh)

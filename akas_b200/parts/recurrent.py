@@ -90,6 +90,7 @@ class GatedLinearAttention(Mixer):
 class DecayedLinearAttention(Mixer):
     takes_normed = True
     chain_safe = True
+    takes_out_dtype = True
 
     @classmethod
     def kernels(cls, spec):
@@ -110,18 +111,20 @@ class DecayedLinearAttention(Mixer):
     def params(self):
         s = self.spec
         c, hd, hv = s.hidden_size, s.num_heads * s.key_dim, s.num_heads * s.value_dim
-        return {
+        p = {
             self._n("q"): Param((hd, c)),
             self._n("k"): Param((hd, c)),
             self._n("v"): Param((hv, c)),
             self._n("g"): Param((hv, c)),
             self._n("o"): Param((c, hv)),
-            self._n("norm"): Param((hv if s.whole_norm else s.value_dim,), role="vector", mean=1.0),
         }
+        if getattr(s, "norm_weight", True):
+            p[self._n("norm")] = Param((hv if s.whole_norm else s.value_dim,), role="vector", mean=1.0)
+        return p
 
     def load(self, get):
         self.w_in = stack_rows([get(self._n(n)) for n in ("q", "k", "v", "g")])
-        self.norm = get(self._n("norm"))
+        self.norm = get(self._n("norm")) if getattr(self.spec, "norm_weight", True) else None
         self.w_out = get(self._n("o"))
         # the decays are constants of the configuration, kept as float32 (the recurrence's own precision)
         self.decay = torch.tensor([float(d) for d in self.spec.decay], dtype=torch.float64).to(
@@ -143,9 +146,9 @@ class DecayedLinearAttention(Mixer):
         return ops.gated_rmsnorm(o, self.norm, s.norm_eps, gate, heads, width, self.rt.dtype,
                                  gate_activation=s.gate_activation, out=out, out_scale=out_scale)
 
-    def forward(self, x, ctx, cache=None, residual=None, write=True):
+    def forward(self, x, ctx, cache=None, residual=None, write=True, out_dtype=None):
         y = self.core(project(self.rt, x, self.w_in), ctx, cache, write)
-        return project(self.rt, y, self.w_out, residual=residual)
+        return project(self.rt, y, self.w_out, out_dtype=out_dtype, residual=residual)
 
 
 class GatedDelta(Mixer):

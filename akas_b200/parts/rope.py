@@ -27,6 +27,22 @@ def slow_long_waves(freq: torch.Tensor, factor: float, low: float, high: float, 
     return torch.where(wave > original / low, freq / factor, torch.where(wave < original / high, freq, blended))
 
 
+def blend_by_index(freq: torch.Tensor, theta: float, rotary: int, factor: float, original: float, fast: float,
+                   slow: float) -> torch.Tensor:
+    """The rates of rotary pairs blended by the pair's index (float64, on the host): with
+    d(t) = rotary ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(d(fast)), 0), hi = min(ceil(d(slow)), rotary - 1)
+    and r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), pair i turns at r_i f_i / factor + (1 - r_i) f_i: the pairs
+    below lo keep their rate, those above hi turn ``factor`` times slower."""
+
+    def d(turns: float) -> float:
+        return rotary * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(theta))
+
+    lo, hi = max(math.floor(d(fast)), 0), min(math.ceil(d(slow)), rotary - 1)
+    i = torch.arange(freq.numel(), dtype=torch.float64)
+    r = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+    return freq / factor * r + freq * (1.0 - r)
+
+
 class Rope(Part):
     chain_safe = True
 
@@ -40,15 +56,25 @@ class Rope(Part):
         scaling = getattr(spec, "scaling", None)
         if scaling is not None:
             freq = slow_long_waves(freq, *scaling)
+        linear, blend = getattr(spec, "linear_factor", None), getattr(spec, "blend", None)
+        if linear is not None:
+            freq = freq / float(linear)
+        if blend is not None:
+            freq = blend_by_index(freq, float(spec.theta), rotary, *blend)
+        self.amplitude = float(getattr(spec, "amplitude", 1.0))
         self.inv_freq = freq.to(runtime.device)
-        self.key = ("rope", rotary, float(spec.theta), scaling)  # the tables are the same for both pairings
+        # the tables are the same for both pairings
+        self.key = ("rope", rotary, float(spec.theta), scaling, linear, blend, self.amplitude)
         self.interleaved = bool(getattr(spec, "interleaved", False))
 
     def tables(self, ctx):
         """(cos, sin), float32 [N, rotary/2], for the tokens of this step."""
         cached = ctx.memo.get(self.key)
         if cached is None:
-            cached = self.rt.ops.rope_tables(ctx.positions, self.inv_freq)
+            if self.amplitude != 1.0:
+                cached = self.rt.ops.rope_tables(ctx.positions, self.inv_freq, self.amplitude)
+            else:
+                cached = self.rt.ops.rope_tables(ctx.positions, self.inv_freq)
             ctx.memo[self.key] = cached
         return cached
 
