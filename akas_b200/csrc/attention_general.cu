@@ -123,7 +123,7 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
                          const int* __restrict__ positions, T* __restrict__ out, float scale, int window, int keep_first,
                          float cap, const float* __restrict__ r1, const float* __restrict__ r2, int sink,
                          const TG* __restrict__ gate, long long ldg, int page_size, int H, int G, int D, int V, int row_words,
-                         const float* __restrict__ sinks, float out_scale, long long ldo, long long vpitch) {
+                         const float* __restrict__ sinks, float out_scale, long long ldo, long long vpitch, int gate_channels) {
   extern __shared__ __align__(16) float smem[];
   const int n = blockIdx.x, g = blockIdx.y;
   const int req = seq_of_token[n];
@@ -248,7 +248,8 @@ attention_general_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, 
         if (a < heads) {
           const int h = g * group + h0 + a;
           float o = l_run[a] > 0.f ? acc[a * Vp + c] / l_run[a] : 0.f;
-          if (gate != nullptr) o *= 1.f / (1.f + expf(-to_f32(gate[(size_t)n * ldg + h])));
+          // one logit per head, or (gate_channels) one per channel of the token's output row
+          if (gate != nullptr) o *= 1.f / (1.f + expf(-to_f32(gate[(size_t)n * ldg + (gate_channels ? (size_t)h * V + c : (size_t)h)])));
           out[(size_t)n * ldo + (size_t)h * V + c] = from_f32<T>(o * out_scale);
         }
       }
@@ -285,7 +286,7 @@ static int launch_general(const void* q, const void* k_pool, const void* v_pool,
                           const int* seq_of_token, const int* positions, void* out, float scale, int window, int keep_first,
                           float cap, const float* r1, const float* r2, int sink, const void* gate, long long ldg,
                           int page_size, int N, int H, int G, int D, int V, const float* sinks, float out_scale,
-                          long long ldo, long long vpitch, cudaStream_t stream) {
+                          long long ldo, long long vpitch, int gate_channels, cudaStream_t stream) {
   const int Vp = (V + kTile - 1) / kTile * kTile;
   const int row_words = (kMaxGroup * D + kMaxGroup * kTile + kMaxGroup * 4 + kMaxGroup * 2 + kMaxGroup * Vp + 1) / 2 * 2;
   const size_t smem = sizeof(float) * (size_t)row_words + sizeof(long long) * kTile;
@@ -300,7 +301,7 @@ static int launch_general(const void* q, const void* k_pool, const void* v_pool,
   }
   return launch_ordinary(attention_general_kernel<T, TG>, dim3(N, G), dim3(kTile), smem, stream, (const T*)q, (const T*)k_pool,
                         (const T*)v_pool, block_table, max_blocks, seq_of_token, positions, (T*)out, scale, window, keep_first,
-                        cap, r1, r2, sink, (const TG*)gate, ldg, page_size, H, G, D, V, row_words, sinks, out_scale, ldo, vpitch);
+                        cap, r1, r2, sink, (const TG*)gate, ldg, page_size, H, G, D, V, row_words, sinks, out_scale, ldo, vpitch, gate_channels);
 }
 
 AKAS_API int akas_attention_general(const void* q, const void* k_pool, const void* v_pool, const int* block_table,
@@ -308,12 +309,12 @@ AKAS_API int akas_attention_general(const void* q, const void* k_pool, const voi
                                     int window, int keep_first, float cap, const float* r1, const float* r2, int sink,
                                     const void* gate, long long ldg, int page_size, int N, int H, int G, int D, int V,
                                     int dtype, const float* sinks, float out_scale, long long ldo, long long vpitch,
-                                    cudaStream_t stream) {
+                                    int gate_channels, cudaStream_t stream) {
   if (N <= 0) return 0;
   if (G <= 0 || H % G || vpitch < V) return (int)cudaErrorInvalidValue;
   if (dtype == AKAS_F32)
     return launch_general<float, float>(q, k_pool, v_pool, block_table, max_blocks, seq_of_token, positions, out, scale, window,
-                                        keep_first, cap, r1, r2, sink, gate, ldg, page_size, N, H, G, D, V, sinks, out_scale, ldo, vpitch, stream);
+                                        keep_first, cap, r1, r2, sink, gate, ldg, page_size, N, H, G, D, V, sinks, out_scale, ldo, vpitch, gate_channels, stream);
   return launch_general<bf16, bf16>(q, k_pool, v_pool, block_table, max_blocks, seq_of_token, positions, out, scale, window,
-                                    keep_first, cap, r1, r2, sink, gate, ldg, page_size, N, H, G, D, V, sinks, out_scale, ldo, vpitch, stream);
+                                    keep_first, cap, r1, r2, sink, gate, ldg, page_size, N, H, G, D, V, sinks, out_scale, ldo, vpitch, gate_channels, stream);
 }

@@ -53,7 +53,12 @@ struct Options {
   float out_scale;
   long long ldo;       // elements between the output rows of two tokens
   long long vpitch;    // elements between two value rows in the pages (V, or more where a row holds more than the value)
+  int gate_channels;   // the gate has one logit per output channel [H * V] of a token, not one per head [H]
 };
+
+__device__ __forceinline__ float gate_of(const Options& opt, size_t token, int head, int V, int c) {
+  return 1.f / (1.f + __expf(-to_f32(opt.gate[token * opt.ldg + (size_t)head * V + c])));
+}
 
 constexpr int kTableBefore = 128, kTableAfter = 192;  // entries of the penalty table on either side of the window's distances
 
@@ -304,13 +309,20 @@ general_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
     if (row >= rows) continue;
     float inv = l_run[h2] > 0.f ? 1.f / l_run[h2] : 0.f;
     const size_t token = packed ? q0 : q0 + row;
-    if (opt.gate != nullptr) inv *= 1.f / (1.f + __expf(-to_f32(opt.gate[token * opt.ldg + head2[h2]])));
+    const bool by_channel = opt.gate != nullptr && opt.gate_channels;
+    if (opt.gate != nullptr && !by_channel) inv *= 1.f / (1.f + __expf(-to_f32(opt.gate[token * opt.ldg + head2[h2]])));
     inv *= opt.out_scale;
     bf16* dst = out + token * opt.ldo + (size_t)head2[h2] * V;
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb)
-      if (nb * 8 + 2 * t < V)
-        *reinterpret_cast<uint32_t*>(dst + nb * 8 + 2 * t) = pack_bf16(o[nb][h2 * 2] * inv, o[nb][h2 * 2 + 1] * inv);
+      if (nb * 8 + 2 * t < V) {
+        float a = o[nb][h2 * 2] * inv, b = o[nb][h2 * 2 + 1] * inv;
+        if (by_channel) {
+          a *= gate_of(opt, token, head2[h2], V, nb * 8 + 2 * t);
+          b *= gate_of(opt, token, head2[h2], V, nb * 8 + 2 * t + 1);
+        }
+        *reinterpret_cast<uint32_t*>(dst + nb * 8 + 2 * t) = pack_bf16(a, b);
+      }
   }
 }
 
@@ -349,15 +361,17 @@ __global__ void general_merge_kernel(const float* __restrict__ partial, const in
     for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
     const float denom = part + (sunk ? exp2f(sink2 - top) : 0.f);
     float inv = denom > 0.f ? opt.out_scale / denom : 0.f;
-    if (opt.gate != nullptr) inv *= 1.f / (1.f + __expf(-to_f32(opt.gate[(size_t)token * opt.ldg + head])));
+    if (opt.gate != nullptr && !opt.gate_channels) inv *= 1.f / (1.f + __expf(-to_f32(opt.gate[(size_t)token * opt.ldg + head])));
     if (lane == 0) inv_s = inv;
   }
   __syncthreads();
   const float inv = inv_s;
+  const bool by_channel = opt.gate != nullptr && opt.gate_channels;
   for (int c = threadIdx.x; c < V; c += blockDim.x) {
     float acc = 0.f;
 #pragma unroll 8
     for (int z = 0; z < splits; ++z) acc = fmaf(src[(size_t)z * (V + 2) + c], factor[z], acc);
+    if (by_channel) acc *= gate_of(opt, (size_t)token, head, V, c);
     out[(size_t)token * opt.ldo + (size_t)head * V + c] = __float2bfloat16_rn(acc * inv);
   }
 }
@@ -401,7 +415,7 @@ AKAS_API int akas_attention_general_tc(const void* q, const void* k_pool, const 
                                        int window, int keep_first, float cap, const float* r1, const float* r2, int sink,
                                        const void* gate, long long ldg, int page_size, int tiles, int H, int KH, int D, int V,
                                        int R, int packed, const float* sinks, float out_scale, long long ldo, float* partial,
-                                       int splits, long long vpitch, cudaStream_t stream) {
+                                       int splits, long long vpitch, int gate_channels, cudaStream_t stream) {
   if (!akas_attention_general_tc_takes(D, V)) return 3999;
   if (ldo % 2 || vpitch % 8 || vpitch < V) return 3999;
   // parts: packed launches only; partial holds (first token of the launch + R) * H * splits * (V + 2) floats
@@ -409,7 +423,7 @@ AKAS_API int akas_attention_general_tc(const void* q, const void* k_pool, const 
   if (packed && (KH <= 0 || H / KH > BQ || tiles != R)) return 3999;
   if (KH <= 0 || H % KH || tiles > 65535 || R <= 0) return (int)cudaErrorInvalidValue;
   if (tiles <= 0) return 0;
-  const Options opt = {scale, cap, r1, r2, window, keep_first, sink, (const bf16*)gate, ldg, sinks, out_scale, ldo, vpitch};
+  const Options opt = {scale, cap, r1, r2, window, keep_first, sink, (const bf16*)gate, ldg, sinks, out_scale, ldo, vpitch, gate_channels};
   const int dk = (D + 31) / 32, dv = (V + 31) / 32;
 #define AKAS_TC(A, B)                                                                                                   \
   if (dk == A && dv == B)                                                                                               \

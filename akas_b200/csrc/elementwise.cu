@@ -378,7 +378,8 @@ AKAS_API int akas_polynorm(const void* z, const float* coeffs, float eps, void* 
 
 // Dynamic Tanh, a norm without statistics: y[m, c] = tanh(alpha * x[row(m), c]) * w[c] + b[c], float32 throughout,
 // rounded once on the way out. alpha is one number on the device. rows: optional gather of the rows to norm.
-template <typename TO>
+// ADD (float32 y only): y += the result, the norm behind a sublayer and the residual sum in one pass.
+template <typename TO, bool ADD>
 __global__ void dynamic_tanh_kernel(const float* __restrict__ x, const float* __restrict__ alpha, const float* __restrict__ w,
                                     const float* __restrict__ b, TO* __restrict__ y, const int* __restrict__ rows, int C,
                                     size_t total) {
@@ -391,6 +392,15 @@ __global__ void dynamic_tanh_kernel(const float* __restrict__ x, const float* __
     const size_t src = (rows != nullptr ? (size_t)rows[m] : m) * C + c;
     const float4 v = *reinterpret_cast<const float4*>(x + src);
     const float4 wv = *reinterpret_cast<const float4*>(w + c), bv = *reinterpret_cast<const float4*>(b + c);
+    if constexpr (ADD) {
+      float4 r = *reinterpret_cast<const float4*>(y + i);
+      r.x += fmaf(tanhf(a * v.x), wv.x, bv.x);
+      r.y += fmaf(tanhf(a * v.y), wv.y, bv.y);
+      r.z += fmaf(tanhf(a * v.z), wv.z, bv.z);
+      r.w += fmaf(tanhf(a * v.w), wv.w, bv.w);
+      *reinterpret_cast<float4*>(y + i) = r;
+      return;
+    }
     y[i] = from_f32<TO>(fmaf(tanhf(a * v.x), wv.x, bv.x));
     y[i + 1] = from_f32<TO>(fmaf(tanhf(a * v.y), wv.y, bv.y));
     y[i + 2] = from_f32<TO>(fmaf(tanhf(a * v.z), wv.z, bv.z));
@@ -401,17 +411,21 @@ __global__ void dynamic_tanh_kernel(const float* __restrict__ x, const float* __
     const size_t m = j / C;
     const int c = (int)(j % C);
     const size_t src = (rows != nullptr ? (size_t)rows[m] : m) * C + c;
-    y[j] = from_f32<TO>(fmaf(tanhf(a * x[src]), w[c], b[c]));
+    const float value = fmaf(tanhf(a * x[src]), w[c], b[c]);
+    if constexpr (ADD) y[j] += value;
+    else y[j] = from_f32<TO>(value);
   }
 }
 
 AKAS_API int akas_dynamic_tanh(const float* x, const float* alpha, const float* w, const float* b, void* y, const int* rows,
-                               int M, int C, int out_dtype, cudaStream_t stream) {
+                               int M, int C, int out_dtype, int add, cudaStream_t stream) {
   const size_t total = (size_t)M * C;
   if (total == 0) return 0;
+  if (add && out_dtype != AKAS_F32) return (int)cudaErrorInvalidValue;
   const unsigned blocks = (unsigned)((total + 1023) / 1024);
-  if (out_dtype == AKAS_F32) dynamic_tanh_kernel<float><<<blocks, 256, 0, stream>>>(x, alpha, w, b, (float*)y, rows, C, total);
-  else dynamic_tanh_kernel<bf16><<<blocks, 256, 0, stream>>>(x, alpha, w, b, (bf16*)y, rows, C, total);
+  if (add) dynamic_tanh_kernel<float, true><<<blocks, 256, 0, stream>>>(x, alpha, w, b, (float*)y, rows, C, total);
+  else if (out_dtype == AKAS_F32) dynamic_tanh_kernel<float, false><<<blocks, 256, 0, stream>>>(x, alpha, w, b, (float*)y, rows, C, total);
+  else dynamic_tanh_kernel<bf16, false><<<blocks, 256, 0, stream>>>(x, alpha, w, b, (bf16*)y, rows, C, total);
   return launch_status();
 }
 
@@ -421,6 +435,36 @@ AKAS_API int akas_dynamic_tanh(const float* x, const float* alpha, const float* 
 // (res[n, c] += res_bias[c], float32 [N, C]) where one is given, so that product can accumulate into it.
 __device__ __forceinline__ float gelu_tanh_f32(float z) {
   return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// An activation without a gate on a product's rows: out[n, f] = act(z[n, f]) for z float32 or bfloat16 with a row
+// pitch, act the square of max(z, 0) (0), the tanh form of gelu (1) or silu (2); float32 until the one rounding.
+template <typename TI, typename TO>
+__global__ void activation_kernel(const TI* __restrict__ z, long long ld, TO* __restrict__ out, int N, int F, int act) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)N * F) return;
+  const size_t n = i / F;
+  const int f = (int)(i % F);
+  const float v = to_f32(z[n * ld + f]);
+  float a;
+  if (act == 0) { const float r = fmaxf(v, 0.f); a = r * r; }
+  else if (act == 1) a = gelu_tanh_f32(v);
+  else a = v / (1.f + expf(-v));
+  out[i] = from_f32<TO>(a);
+}
+
+AKAS_API int akas_activation(const void* z, long long ld, int in_dtype, void* out, int out_dtype, int N, int F, int act,
+                             cudaStream_t stream) {
+  if (N <= 0 || F <= 0) return 0;
+  if (act < 0 || act > 2) return (int)cudaErrorInvalidValue;
+  const unsigned blocks = (unsigned)(((size_t)N * F + 255) / 256);
+#define AKAS_ACT(TI, TO) activation_kernel<TI, TO><<<blocks, 256, 0, stream>>>((const TI*)z, ld, (TO*)out, N, F, act)
+  if (in_dtype == AKAS_F32 && out_dtype == AKAS_F32) AKAS_ACT(float, float);
+  else if (in_dtype == AKAS_F32) AKAS_ACT(float, bf16);
+  else if (out_dtype == AKAS_F32) AKAS_ACT(bf16, float);
+  else AKAS_ACT(bf16, bf16);
+#undef AKAS_ACT
+  return launch_status();
 }
 
 template <typename TO>

@@ -290,7 +290,9 @@ AKAS_API int akas_latent_norm_store(const float* proj, long long ld, int QR, int
                                     const int* block_table, int max_blocks, const int* seq_of_token, const int* positions,
                                     int page_size, int N, int write, int dtype, cudaStream_t stream) {
   if (N <= 0) return 0;
-  if (QR <= 0 || KR <= 0 || rot < 0 || (cos_t != nullptr && rot % 2)) return (int)cudaErrorInvalidValue;
+  // QR 0: there is no query latent (queries that are a projection of their own); only the cached row is made
+  if (QR < 0 || (QR > 0 && qw == nullptr) || KR <= 0 || rot < 0 || (cos_t != nullptr && rot % 2)) return (int)cudaErrorInvalidValue;
+  if (QR == 0 && !write) return 0;
   if (dtype == AKAS_F32)
     return launch_ordinary(latent_norm_store_kernel<float>, dim3(N), dim3(128), 0, stream, proj, ld, QR, KR, rot, qw, kw, eps,
                            cos_t, sin_t, interleaved, (float*)q_out, (float*)pool, block_table, max_blocks, seq_of_token,

@@ -5,13 +5,18 @@
 // form `groups` equal groups of neighbours, a group's score is its largest choice score, only outputs of the `keep`
 // best groups can be chosen; the `top` largest choice scores among those are chosen (ties: the lower index); the
 // weights are the chosen outputs' s over their sum (+ 1e-20). Router outputs from `experts` on are identity experts:
-// they have no matrices and return their input.
+// they have no matrices and return their input. Options: `sigmoid`, s = 1 / (1 + exp(-z)) per output instead of the
+// softmax; no correction (a null pointer); `renorm` 0, the weights are the chosen s as they are; `extra` more rows of
+// W_r behind the R that compete, whose sigmoids are returned beside the choice (gates that read the router's input).
 //
 // Experts, token by token (moe_gate_up, moe_down): act[pair] = silu(W_gate h) * (W_up h) for every (token, chosen
 // real expert) pair, then out[n] = sum over the token's chosen outputs of weight * (W_down act, or h for an identity
 // expert), added in the order of the choice. Every output is one warp's sum over the inner size in a fixed order, so
 // a token's result does not depend on what else the step holds. Weights of all experts are stacked: gate and up as
-// [experts, 2 F, C] (gate rows first), down as [experts, C, F].
+// [experts, 2 F, C] (gate rows first), down as [experts, C, F]. Where the weight multiplies the expert's INPUT
+// (out[n] = sum expert(w h)), moe_gate_up gets the weights and scales both of its float32 sums (W (w h) = w (W h))
+// before the activation, and moe_down gets none. moe_down can also add a dense result of every token (a shared
+// expert's), times a gate per token.
 #include "common.cuh"
 
 using namespace akas;
@@ -27,8 +32,10 @@ __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); 
 template <typename T>
 __global__ void __launch_bounds__(kRouteTokens * 32)
 moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict__ w, const float* __restrict__ correction,
-                 int* __restrict__ chosen, float* __restrict__ weights, int N, int C, int R, int groups, int keep, int top) {
+                 int* __restrict__ chosen, float* __restrict__ weights, int N, int C, int RC, int groups, int keep, int top,
+                 int sigmoid, int renorm, int extra, float* __restrict__ extras) {
   extern __shared__ __align__(16) float smem[];
+  int R = RC + extra;                              // rows of the matrix: the RC outputs that compete, then the extra ones
   float* rows = smem;                              // [kRouteTokens][kRouteChunk]
   float* z = rows + kRouteTokens * kRouteChunk;    // [kRouteTokens][R] logits, then scores
   float* pick = z + kRouteTokens * R;              // [kRouteTokens][R] choice scores
@@ -138,20 +145,29 @@ moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict
   float* zt = z + warp * R;
   float* pt = pick + warp * R;
   float* gt = gbest + warp * groups;
-  float top_z = -INFINITY;
-  for (int e = lane; e < R; e += 32) top_z = fmaxf(top_z, zt[e]);
-  top_z = warp_max(top_z);
-  float sum = 0.f;
-  for (int e = lane; e < R; e += 32) {
-    const float p = expf(zt[e] - top_z);
-    zt[e] = p;
-    sum += p;
-  }
-  sum = warp_sum(sum);
-  const float inv = 1.f / sum;
-  for (int e = lane; e < R; e += 32) {
-    zt[e] *= inv;
-    pt[e] = zt[e] + correction[e];
+  for (int j = lane; j < extra; j += 32) extras[(size_t)n * extra + j] = 1.f / (1.f + expf(-zt[RC + j]));
+  R = RC;  // from here on: the outputs that compete
+  if (sigmoid) {
+    for (int e = lane; e < R; e += 32) {
+      zt[e] = 1.f / (1.f + expf(-zt[e]));
+      pt[e] = zt[e] + (correction != nullptr ? correction[e] : 0.f);
+    }
+  } else {
+    float top_z = -INFINITY;
+    for (int e = lane; e < R; e += 32) top_z = fmaxf(top_z, zt[e]);
+    top_z = warp_max(top_z);
+    float sum = 0.f;
+    for (int e = lane; e < R; e += 32) {
+      const float p = expf(zt[e] - top_z);
+      zt[e] = p;
+      sum += p;
+    }
+    sum = warp_sum(sum);
+    const float inv = 1.f / sum;
+    for (int e = lane; e < R; e += 32) {
+      zt[e] *= inv;
+      pt[e] = zt[e] + (correction != nullptr ? correction[e] : 0.f);
+    }
   }
   __syncwarp();
   const int size = R / groups;
@@ -192,23 +208,25 @@ moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict
     total += zt[at];
     __syncwarp();
   }
-  if (lane == 0) {
+  if (lane == 0 && renorm) {
     const float norm = 1.f / (total + 1e-20f);
     for (int k = 0; k < top; ++k) weights[(size_t)n * top + k] *= norm;
   }
 }
 
 // One warp per (pair, hidden channel f): both dots over C, act = silu(gate) * up. Pairs of identity experts do nothing.
+// in_weights (or null): the pair's weight multiplies both sums before the activation.
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_gate_up_kernel(const T* __restrict__ h, long long ldh, const T* __restrict__ w_gate_up, const int* __restrict__ chosen,
-                   T* __restrict__ act, int pairs, int top, int C, int F, int experts) {
+                   T* __restrict__ act, int pairs, int top, int C, int F, int experts, const float* __restrict__ in_weights) {
   const int pair = blockIdx.x;
   const int e = chosen[pair];
   if (e >= experts || e < 0) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   const T* x = h + (size_t)(pair / top) * ldh;
   const T* wg = w_gate_up + (size_t)e * 2 * F * C;
+  const float scale = in_weights != nullptr ? in_weights[pair] : 1.f;
   constexpr int N = Vec<T>::N;
   const bool vec = C % N == 0 && ldh % N == 0 && ((uintptr_t)h % 16) == 0 && ((uintptr_t)w_gate_up % 16) == 0;
   for (int f = blockIdx.y * warps + warp; f < F; f += gridDim.y * warps) {
@@ -231,21 +249,23 @@ moe_gate_up_kernel(const T* __restrict__ h, long long ldh, const T* __restrict__
         au = fmaf(xv, to_f32(u_row[c]), au);
       }
     }
-    ag = warp_sum(ag);
-    au = warp_sum(au);
+    ag = warp_sum(ag) * scale;
+    au = warp_sum(au) * scale;
     if (lane == 0) act[(size_t)pair * F + f] = from_f32<T>(silu_f(ag) * au);
   }
 }
 
 // One warp per (token, output channel c): the weighted sum over the token's chosen outputs. With `x` the sum does not
 // go to `out` but into the residual stream: x += mult * (ls_a * a + ls_b * sum), the update of a block whose mixer's
-// result a and feed-forward meet the stream together (a null scale is all ones).
+// result a and feed-forward meet the stream together (a null scale is all ones). Null weights: every weight is one.
+// shared (or null): float32 [N, C] added to the sum, times shared_gate[n * ldsg] where that is given.
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_down_kernel(const T* __restrict__ h, long long ldh, const T* __restrict__ w_down, const int* __restrict__ chosen,
                 const float* __restrict__ weights, const T* __restrict__ act, float* __restrict__ out, int top, int C, int F,
                 int experts, float* __restrict__ x, const float* __restrict__ a_res, const float* __restrict__ ls_a,
-                const float* __restrict__ ls_b, float mult) {
+                const float* __restrict__ ls_b, float mult, const float* __restrict__ shared,
+                const float* __restrict__ shared_gate, long long ldsg) {
   const int n = blockIdx.x;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
   constexpr int N = Vec<T>::N;
@@ -254,7 +274,7 @@ moe_down_kernel(const T* __restrict__ h, long long ldh, const T* __restrict__ w_
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
       const int e = chosen[(size_t)n * top + k];
-      const float g = weights[(size_t)n * top + k];
+      const float g = weights != nullptr ? weights[(size_t)n * top + k] : 1.f;
       if (e >= experts) {
         total = fmaf(g, to_f32(h[(size_t)n * ldh + c]), total);
         continue;
@@ -276,6 +296,7 @@ moe_down_kernel(const T* __restrict__ h, long long ldh, const T* __restrict__ w_
       total = fmaf(g, warp_sum(acc), total);
     }
     if (lane == 0) {
+      if (shared != nullptr) total = fmaf(shared_gate != nullptr ? shared_gate[(size_t)n * ldsg] : 1.f, shared[(size_t)n * C + c], total);
       if (x != nullptr) {
         const size_t at = (size_t)n * C + c;
         x[at] = fmaf(mult, fmaf(ls_b ? ls_b[c] : 1.f, total, (ls_a ? ls_a[c] : 1.f) * a_res[at]), x[at]);
@@ -288,12 +309,15 @@ moe_down_kernel(const T* __restrict__ h, long long ldh, const T* __restrict__ w_
 
 }  // namespace
 
+// R: the outputs that compete; the matrix has R + extra rows.
 AKAS_API int akas_moe_route(const void* h, long long ldh, const float* w, const float* correction, int* chosen, float* weights,
-                            int N, int C, int R, int groups, int keep, int top, int dtype, cudaStream_t stream) {
+                            int N, int C, int R, int groups, int keep, int top, int dtype, int sigmoid, int renorm, int extra,
+                            float* extras, cudaStream_t stream) {
   if (N <= 0) return 0;
-  if (R <= 0 || groups <= 0 || R % groups || keep <= 0 || keep > groups || top <= 0 || top > keep * (R / groups))
+  if (R <= 0 || groups <= 0 || R % groups || keep <= 0 || keep > groups || top <= 0 || top > keep * (R / groups) || extra < 0 ||
+      (extra > 0 && extras == nullptr))
     return (int)cudaErrorInvalidValue;
-  const size_t smem = sizeof(float) * ((size_t)kRouteTokens * kRouteChunk + 2 * (size_t)kRouteTokens * R + (size_t)kRouteTokens * groups +
+  const size_t smem = sizeof(float) * ((size_t)kRouteTokens * kRouteChunk + 2 * (size_t)kRouteTokens * (R + extra) + (size_t)kRouteTokens * groups +
                                        (size_t)kRouteTokens * kRouteOutputs * kRouteTokens);
   if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
   const dim3 grid((N + kRouteTokens - 1) / kRouteTokens);
@@ -310,32 +334,33 @@ AKAS_API int akas_moe_route(const void* h, long long ldh, const float* w, const 
   }
   if (dtype == AKAS_F32)
     return launch_ordinary(moe_route_kernel<float>, grid, dim3(kRouteTokens * 32), smem, stream, (const float*)h, ldh, w,
-                           correction, chosen, weights, N, C, R, groups, keep, top);
+                           correction, chosen, weights, N, C, R, groups, keep, top, sigmoid, renorm, extra, extras);
   return launch_ordinary(moe_route_kernel<bf16>, grid, dim3(kRouteTokens * 32), smem, stream, (const bf16*)h, ldh, w, correction,
-                         chosen, weights, N, C, R, groups, keep, top);
+                         chosen, weights, N, C, R, groups, keep, top, sigmoid, renorm, extra, extras);
 }
 
 AKAS_API int akas_moe_gate_up(const void* h, long long ldh, const void* w_gate_up, const int* chosen, void* act, int N,
-                              int top, int C, int F, int experts, int dtype, cudaStream_t stream) {
+                              int top, int C, int F, int experts, int dtype, const float* in_weights, cudaStream_t stream) {
   if (N <= 0 || top <= 0 || experts <= 0) return 0;
   const int pairs = N * top;
   // warps enough to fill the GPU when the pairs are few (a row of F per warp), fewer and longer-lived when they are many
   const dim3 grid(pairs, max(1, min((F + 7) / 8, pairs >= 4096 ? 2 : pairs >= 256 ? 16 : 256)));
   if (dtype == AKAS_F32)
     return launch_ordinary(moe_gate_up_kernel<float>, grid, dim3(256), 0, stream, (const float*)h, ldh, (const float*)w_gate_up,
-                           chosen, (float*)act, pairs, top, C, F, experts);
+                           chosen, (float*)act, pairs, top, C, F, experts, in_weights);
   return launch_ordinary(moe_gate_up_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)h, ldh, (const bf16*)w_gate_up,
-                         chosen, (bf16*)act, pairs, top, C, F, experts);
+                         chosen, (bf16*)act, pairs, top, C, F, experts, in_weights);
 }
 
 AKAS_API int akas_moe_down(const void* h, long long ldh, const void* w_down, const int* chosen, const float* weights,
                            const void* act, float* out, int N, int top, int C, int F, int experts, int dtype, float* x,
-                           const float* a_res, const float* ls_a, const float* ls_b, float mult, cudaStream_t stream) {
+                           const float* a_res, const float* ls_a, const float* ls_b, float mult, const float* shared,
+                           const float* shared_gate, long long ldsg, cudaStream_t stream) {
   if (N <= 0) return 0;
   const dim3 grid(N, max(1, min((C + 7) / 8, N >= 2048 ? 2 : N >= 64 ? 32 : 256)));
   if (dtype == AKAS_F32)
     return launch_ordinary(moe_down_kernel<float>, grid, dim3(256), 0, stream, (const float*)h, ldh, (const float*)w_down, chosen,
-                           weights, (const float*)act, out, top, C, F, experts, x, a_res, ls_a, ls_b, mult);
+                           weights, (const float*)act, out, top, C, F, experts, x, a_res, ls_a, ls_b, mult, shared, shared_gate, ldsg);
   return launch_ordinary(moe_down_kernel<bf16>, grid, dim3(256), 0, stream, (const bf16*)h, ldh, (const bf16*)w_down, chosen,
-                         weights, (const bf16*)act, out, top, C, F, experts, x, a_res, ls_a, ls_b, mult);
+                         weights, (const bf16*)act, out, top, C, F, experts, x, a_res, ls_a, ls_b, mult, shared, shared_gate, ldsg);
 }

@@ -64,26 +64,47 @@ moe_plan_kernel(const int* __restrict__ chosen, int pairs, int experts, int* __r
   }
 }
 
+// in_weights (or null): the pair's weight multiplies its copy of the token's row (the weight on an expert's input),
+// in float32, rounded once.
 __global__ void moe_gather_kernel(const bf16* __restrict__ h, long long ldh, const int* __restrict__ row_of_pair,
-                                  bf16* __restrict__ sorted, int top, int C) {
+                                  bf16* __restrict__ sorted, int top, int C, const float* __restrict__ in_weights) {
   const int pair = blockIdx.x;
   const int row = row_of_pair[pair];
   if (row < 0) return;
   const uint4* src = reinterpret_cast<const uint4*>(h + (size_t)(pair / top) * ldh);
   uint4* dst = reinterpret_cast<uint4*>(sorted + (size_t)row * C);
-  for (int i = threadIdx.x; i < C / 8; i += blockDim.x) dst[i] = src[i];
+  if (in_weights == nullptr) {
+    for (int i = threadIdx.x; i < C / 8; i += blockDim.x) dst[i] = src[i];
+    return;
+  }
+  const float g = in_weights[pair];
+  for (int i = threadIdx.x; i < C / 8; i += blockDim.x) {
+    float v[8];
+    load_vec(reinterpret_cast<const bf16*>(src + i), v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] *= g;
+    store_vec(reinterpret_cast<bf16*>(dst + i), v);
+  }
 }
 
 __global__ void moe_combine_kernel(const bf16* __restrict__ h, long long ldh, const float* __restrict__ y,
                                    const int* __restrict__ row_of_pair, const float* __restrict__ weights,
                                    float* __restrict__ out, int top, int C, float* __restrict__ x, const float* __restrict__ a_res,
-                                   const float* __restrict__ ls_a, const float* __restrict__ ls_b, float mult) {
+                                   const float* __restrict__ ls_a, const float* __restrict__ ls_b, float mult,
+                                   const float* __restrict__ shared, const float* __restrict__ shared_gate, long long ldsg) {
+  // null weights: every weight is one. shared (or null): float32 [N, C] added to the sum, times shared_gate[n * ldsg]
+  // where that is given.
   const int n = blockIdx.x;
   for (int c = threadIdx.x * 4; c < C; c += blockDim.x * 4) {
     float4 total = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (shared != nullptr) {
+      const float sg = shared_gate != nullptr ? shared_gate[(size_t)n * ldsg] : 1.f;
+      const float4 sv = *reinterpret_cast<const float4*>(shared + (size_t)n * C + c);
+      total = make_float4(sg * sv.x, sg * sv.y, sg * sv.z, sg * sv.w);
+    }
     for (int k = 0; k < top; ++k) {
       const int row = row_of_pair[(size_t)n * top + k];
-      const float g = weights[(size_t)n * top + k];
+      const float g = weights != nullptr ? weights[(size_t)n * top + k] : 1.f;
       float4 v;
       if (row >= 0) {
         v = *reinterpret_cast<const float4*>(y + (size_t)row * C + c);
@@ -306,14 +327,14 @@ AKAS_API int akas_moe_grouped_takes(int C, int F, int experts) { return C % 8 ==
 // chosen [N, top] int32 (an expert number >= experts: an identity expert); outputs row_of_pair [N * top], tile_expert
 // [rows_cap / 128], plan [1], sorted [rows_cap, C] bfloat16.
 AKAS_API int akas_moe_sort(const void* h, long long ldh, const int* chosen, int* row_of_pair, int* tile_expert, int* plan,
-                           void* sorted, int N, int top, int C, int experts, cudaStream_t stream) {
+                           void* sorted, int N, int top, int C, int experts, const float* in_weights, cudaStream_t stream) {
   if (N <= 0 || top <= 0) return 0;
   if (!akas_moe_grouped_takes(C, 8, experts) || ldh % 8 || (uintptr_t)h % 16 || (uintptr_t)sorted % 16) return (int)cudaErrorInvalidValue;
   int err = launch_ordinary(moe_plan_kernel, dim3(1), dim3(kPlanThreads), 0, stream, chosen, N * top, experts, row_of_pair,
                             tile_expert, plan);
   if (err) return err;
   return launch_ordinary(moe_gather_kernel, dim3(N * top), dim3(128), 0, stream, (const bf16*)h, ldh, (const int*)row_of_pair,
-                         (bf16*)sorted, top, C);
+                         (bf16*)sorted, top, C, in_weights);
 }
 
 // epilogue 2: x = sorted [rows_cap, K = C], w = [experts, 2F, C] (N = 2F), y = act [rows_cap, F] bfloat16;
@@ -335,12 +356,14 @@ AKAS_API int akas_moe_grouped_gemm(const void* x, const void* w, void* y, const 
 
 AKAS_API int akas_moe_combine(const void* h, long long ldh, const float* y, const int* row_of_pair, const float* weights,
                               float* out, int N, int top, int C, float* x, const float* a_res, const float* ls_a,
-                              const float* ls_b, float mult, cudaStream_t stream) {
+                              const float* ls_b, float mult, const float* shared, const float* shared_gate, long long ldsg,
+                              cudaStream_t stream) {
   if (N <= 0) return 0;
-  if (C % 8 || ldh % 4 || (uintptr_t)h % 8 || (uintptr_t)y % 16 || (uintptr_t)out % 16) return (int)cudaErrorInvalidValue;
+  if (C % 8 || ldh % 4 || (uintptr_t)h % 8 || (uintptr_t)y % 16 || (uintptr_t)out % 16 || (uintptr_t)shared % 16)
+    return (int)cudaErrorInvalidValue;
   if (((uintptr_t)x | (uintptr_t)a_res | (uintptr_t)ls_a | (uintptr_t)ls_b) % 16) return (int)cudaErrorInvalidValue;
   return launch_ordinary(moe_combine_kernel, dim3(N), dim3(C >= 1024 ? 256 : 128), 0, stream, (const bf16*)h, ldh, y, row_of_pair,
-                         weights, out, top, C, x, a_res, ls_a, ls_b, mult);
+                         weights, out, top, C, x, a_res, ls_a, ls_b, mult, shared, shared_gate, ldsg);
 }
 
 AKAS_API int akas_moe_grouped_status() {

@@ -646,7 +646,11 @@ __global__ void delta_prep_kernel(float* __restrict__ y, long long ldy, int G, i
 //
 // One warp per (token, head): out = o / sqrt(mean(o^2) + eps) * w * f(gate) * out_scale, f = silu or (sigmoid != 0)
 // the sigmoid alone; the output's rows have a pitch of their own. A norm over all heads together is the call with one
-// head of H * V channels.
+// head of H * V channels. w may be null: the division alone, every weight one.
+__device__ __forceinline__ float4 norm_weight4(const float* __restrict__ w, int j) {
+  return w != nullptr ? *reinterpret_cast<const float4*>(w + j) : make_float4(1.f, 1.f, 1.f, 1.f);
+}
+
 template <typename TG, typename TO>
 __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* __restrict__ w, float eps,
                                      const TG* __restrict__ gate, long long ldg, TO* __restrict__ out, int N, int H, int V,
@@ -670,7 +674,7 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* _
         const int j = lane * 4 + i * 128;
         if (j < V) {
           x[i] = *reinterpret_cast<const float4*>(row + j);
-          wv[i] = *reinterpret_cast<const float4*>(w + j);
+          wv[i] = norm_weight4(w, j);
           load4(gate + (size_t)n * ldg + (size_t)h * V + j, gv[i]);
           ss = fmaf(x[i].x, x[i].x, ss); ss = fmaf(x[i].y, x[i].y, ss); ss = fmaf(x[i].z, x[i].z, ss); ss = fmaf(x[i].w, x[i].w, ss);
         }
@@ -705,7 +709,7 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* _
     const float inv = out_scale / sqrtf(ss / (float)V + eps);
     for (int j = lane * 4; j < V; j += 128) {
       const float4 x = *reinterpret_cast<const float4*>(row + j);
-      const float4 wv = *reinterpret_cast<const float4*>(w + j);
+      const float4 wv = norm_weight4(w, j);
       float gv[4];
       load4(gate + (size_t)n * ldg + (size_t)h * V + j, gv);
 #pragma unroll
@@ -726,7 +730,7 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const float* _
   const float inv = out_scale / sqrtf(ss / (float)V + eps);
   for (int j = lane; j < V; j += 32) {
     const float gv = to_f32(gate[(size_t)n * ldg + (size_t)h * V + j]);
-    out[(size_t)n * ldo + (size_t)h * V + j] = from_f32<TO>(row[j] * inv * w[j] * (sigmoid ? sigmoid_f(gv) : gv * sigmoid_f(gv)));
+    out[(size_t)n * ldo + (size_t)h * V + j] = from_f32<TO>(row[j] * inv * (w != nullptr ? w[j] : 1.f) * (sigmoid ? sigmoid_f(gv) : gv * sigmoid_f(gv)));
   }
 }
 

@@ -14,7 +14,8 @@
 using namespace akas;
 
 __global__ void rope_tables_kernel(const int* __restrict__ positions, const double* __restrict__ inv_freq,
-                                   float* __restrict__ cos_out, float* __restrict__ sin_out, int N, int half) {
+                                   float* __restrict__ cos_out, float* __restrict__ sin_out, int N, int half,
+                                   float amplitude) {
   chain_release();
   chain_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -31,16 +32,17 @@ __global__ void rope_tables_kernel(const int* __restrict__ positions, const doub
   const float hi = (float)reduced, lo = (float)(reduced - (double)hi);
   float s, c;
   sincosf(hi, &s, &c);
-  cos_out[i] = fmaf(-lo, s, c);
-  sin_out[i] = fmaf(lo, c, s);
+  // (an amplitude other than one scales both tables: a rotation that also stretches)
+  cos_out[i] = amplitude * fmaf(-lo, s, c);
+  sin_out[i] = amplitude * fmaf(lo, c, s);
 }
 
 AKAS_API int akas_rope_tables(const int* positions, const double* inv_freq, float* cos_out, float* sin_out, int N,
-                              int half, cudaStream_t stream) {
+                              int half, float amplitude, cudaStream_t stream) {
   const size_t total = (size_t)N * half;
   if (total == 0) return 0;
   return launch_chained(rope_tables_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, positions,
-                        inv_freq, cos_out, sin_out, N, half);
+                        inv_freq, cos_out, sin_out, N, half, amplitude);
 }
 
 #define AKAS_ROPE_WARPS 4

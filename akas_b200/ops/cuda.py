@@ -39,7 +39,8 @@ _SIGNATURES = {
         "akas_add_rows": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "akas_polynorm": [c_void_p, c_void_p, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "akas_scaled_add": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p],
-        "akas_dynamic_tanh": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "akas_dynamic_tanh": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "akas_activation": [c_void_p, c_longlong, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "akas_gated_activation": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                   c_int, c_void_p],
     },
@@ -52,11 +53,12 @@ _SIGNATURES = {
     },
     "moe": {
         "akas_moe_route": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                           c_int, c_int, c_void_p],
+                           c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p],
         "akas_moe_gate_up": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                             c_void_p],
+                             c_void_p, c_void_p],
         "akas_moe_down": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                          c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p],
+                          c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_longlong,
+                          c_void_p],
     },
     "recurrent": {
         "akas_decay_gates": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_int, c_void_p],
@@ -85,23 +87,23 @@ _SIGNATURES = {
                                c_void_p, c_void_p],
         "akas_attention_general": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_int,
                                    c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
-                                   c_int, c_int, c_int, c_void_p, c_float, c_longlong, c_longlong, c_void_p],
+                                   c_int, c_int, c_int, c_void_p, c_float, c_longlong, c_longlong, c_int, c_void_p],
     },
     "attention_general_tc": {
         "akas_attention_general_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float,
                                       c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int,
                                       c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_longlong, c_void_p, c_int,
-                                      c_longlong, c_void_p],
+                                      c_longlong, c_int, c_void_p],
         "akas_attention_general_tc_takes": [c_int, c_int],
     },
     "moe_grouped": {
         "akas_moe_grouped_rows": [c_int, c_int],
         "akas_moe_grouped_takes": [c_int, c_int, c_int],
         "akas_moe_sort": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                          c_void_p],
+                          c_void_p, c_void_p],
         "akas_moe_grouped_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "akas_moe_combine": [c_void_p, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
-                             c_void_p, c_void_p, c_float, c_void_p],
+                             c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_longlong, c_void_p],
         "akas_moe_grouped_status": [],
     },
     "conv": {
@@ -109,7 +111,7 @@ _SIGNATURES = {
         "akas_short_conv_decode": [c_void_p] * 7 + [c_int] * 5 + [c_void_p],
     },
     "rope": {
-        "akas_rope_tables": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "akas_rope_tables": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
         "akas_qk_norm_rope_store": [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_int,
                                     c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
                                     c_int, c_int, c_int, c_void_p],
@@ -976,12 +978,12 @@ def short_conv(bcx, taps, bias, state, cu_seqlens, seq_of_token, slots, decode_o
     return out
 
 
-def rope_tables(positions, inv_freq):
+def rope_tables(positions, inv_freq, amplitude=1.0):
     n, half = positions.numel(), inv_freq.numel()
     cos = torch.empty((n, half), dtype=torch.float32, device=positions.device)
     sin = torch.empty_like(cos)
-    _check(_fn("rope", "akas_rope_tables")(_ptr(positions), _ptr(inv_freq), _ptr(cos), _ptr(sin), n, half, _stream()),
-           "rope_tables")
+    _check(_fn("rope", "akas_rope_tables")(_ptr(positions), _ptr(inv_freq), _ptr(cos), _ptr(sin), n, half, float(amplitude),
+                                          _stream()), "rope_tables")
     return cos, sin
 
 
@@ -1372,6 +1374,8 @@ def gated_rmsnorm(o, weight, eps, gate, heads, vdim, out_dtype, gate_activation=
         raise ValueError("gated_rmsnorm takes dense float32 o [N, heads * vdim]")
     if gate_activation not in ("silu", "sigmoid"):
         raise ValueError(f"unknown gate activation {gate_activation!r}")
+    if weight is not None and (weight.dtype != torch.float32 or weight.numel() != vdim):
+        raise ValueError("gated_rmsnorm: the weight is float32 [vdim] (None: the division alone)")
     gp, ldg = _rows(gate, "gate")
     if out is None:
         out = torch.empty((n, heads * vdim), dtype=out_dtype, device=o.device)
@@ -1463,8 +1467,10 @@ general_splits = os.environ.get("AKAS_B200_GENERAL_SPLITS", "1") != "0"  # 0: a 
 
 @_flushes
 def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, scale, window, keep_first, softcap,
-                      r1, r2, sink, gate, page_size, ctx=None, sinks=None, out=None, out_scale=1.0, values_in_keys=0):
-    """``values_in_keys`` = V > 0: a key's row holds its value too, as its first V channels; ``v_pool`` is not read."""
+                      r1, r2, sink, gate, page_size, ctx=None, sinks=None, out=None, out_scale=1.0, values_in_keys=0,
+                      gate_channels=False):
+    """``values_in_keys`` = V > 0: a key's row holds its value too, as its first V channels; ``v_pool`` is not read.
+    ``gate_channels``: the gate has one logit per channel of a token's output row [N, heads * value_dim], not one per head."""
     n = q.shape[0]
     kh, d = k_pool.shape[1], k_pool.shape[3]
     if values_in_keys:
@@ -1480,6 +1486,9 @@ def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, s
     if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != heads):
         raise ValueError("attention_general: sinks must be float32 [heads]")
     gp, ldg = _rows(gate, "gate") if gate is not None else (None, 0)
+    if gate is not None and gate.shape != (n, heads * vd if gate_channels else heads):
+        raise ValueError("attention_general: the gate is [N, heads], or with gate_channels [N, heads * value_dim]")
+    channels = int(bool(gate_channels and gate is not None))
     if out is None:
         out = torch.empty((n, heads * vd), dtype=q.dtype, device=q.device)
     elif out.shape != (n, heads * vd) or out.dtype != q.dtype:
@@ -1510,13 +1519,13 @@ def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, s
                 err = _fn("attention_general_tc", "akas_attention_general_tc")(
                     _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table[start:]), block_table.shape[1],
                     _ptr(ctx.cu_seqlens[start:]), _ptr(positions), op, *options, tiles, heads, kh, d, vd, requests,
-                    packed, *tail, _ptr(partial), splits, vpitch, _stream())
+                    packed, *tail, _ptr(partial), splits, vpitch, channels, _stream())
                 _check(err, "attention_general (tensor cores)")
             singles = 0
     if singles:
         _check(_fn("attention_general", "akas_attention_general")(
             _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token), _ptr(positions),
-            op, *options, singles, heads, kh, d, vd, _code(q), *tail, vpitch, _stream()), "attention_general")
+            op, *options, singles, heads, kh, d, vd, _code(q), *tail, vpitch, channels, _stream()), "attention_general")
     return out
 
 
@@ -1524,16 +1533,39 @@ def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, s
 
 
 @_flushes
-def dynamic_tanh(x, alpha, weight, shift, out_dtype, rows=None):
-    """tanh(alpha * x) * weight + shift per element of float32 x [N, C]; ``rows``: int32 indices of the rows to take."""
+def dynamic_tanh(x, alpha, weight, shift, out_dtype, rows=None, residual=None):
+    """tanh(alpha * x) * weight + shift per element of float32 x [N, C]; ``rows``: int32 indices of the rows to take.
+    With ``residual`` (dense float32 [N, C]) the result is added to it in place and it is returned."""
     c = x.shape[-1]
     if x.dtype != torch.float32 or alpha.dtype != torch.float32 or weight.numel() != c or shift.numel() != c:
         raise ValueError("dynamic_tanh takes float32 x [N, C], a float32 alpha and vectors of C numbers")
     _dense(x, "x")
     m = rows.numel() if rows is not None else x.numel() // c
-    out = torch.empty((m, c) if rows is not None else x.shape, dtype=out_dtype, device=x.device)
+    if residual is not None:
+        if rows is not None or residual.dtype != torch.float32 or residual.shape != x.shape or not residual.is_contiguous():
+            raise ValueError("dynamic_tanh adds to a dense float32 residual of x's shape, all rows")
+        out = residual
+    else:
+        out = torch.empty((m, c) if rows is not None else x.shape, dtype=out_dtype, device=x.device)
     _check(_fn("elementwise", "akas_dynamic_tanh")(_ptr(x), _ptr(alpha), _ptr(weight), _ptr(shift), _ptr(out), _ptr(rows), m, c,
-                                                  _CODE[out_dtype], _stream()), "dynamic_tanh")
+                                                  _CODE[out.dtype], int(residual is not None), _stream()), "dynamic_tanh")
+    return out
+
+
+_PLAIN_ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "silu": 2}
+
+
+@_flushes
+def activation(z, kind, out_dtype):
+    """act(z) element by element of a product's rows [N, F] (float32 or bfloat16, rows may be parts of wider rows),
+    float32 until the one rounding to ``out_dtype``."""
+    if kind not in _PLAIN_ACTIVATIONS:
+        raise ValueError(f"unknown activation {kind!r}")
+    n, f = z.shape
+    zp, ld = _rows(z, "z")
+    out = torch.empty((n, f), dtype=out_dtype, device=z.device)
+    _check(_fn("elementwise", "akas_activation")(zp, ld, _code(z), _ptr(out), _CODE[out_dtype], n, f, _PLAIN_ACTIVATIONS[kind],
+                                                _stream()), "activation")
     return out
 
 
@@ -1574,7 +1606,7 @@ def latent_norm_store(proj, q_rank, kv_rank, rot, q_weight, kv_weight, eps, cos,
         raise ValueError("latent_norm_store takes the float32 product [N, >= q_rank + kv_rank + rot]")
     if pool.shape[1] != 1 or pool.shape[3] != kv_rank + rot or not pool.is_contiguous():
         raise ValueError("latent_norm_store: pages are [pages, 1, page, kv_rank + rot]")
-    if q_weight.numel() != q_rank or kv_weight.numel() != kv_rank:
+    if (q_weight.numel() if q_weight is not None else 0) != q_rank or kv_weight.numel() != kv_rank:
         raise ValueError("latent_norm_store: one norm weight per latent channel")
     if cos is not None:
         if not rot or cos.dtype != torch.float32 or cos.shape != (n, rot // 2) or sin.shape != cos.shape:
@@ -1616,18 +1648,25 @@ def head_linear(x, w, heads, gate=None, cos=None, sin=None, interleaved=False):
 
 
 @_flushes
-def moe_route(h, w_router, correction, groups, keep, top):
+def moe_route(h, w_router, correction, groups, keep, top, scoring="softmax", renormalize=True, extra=0):
+    """``extra`` = X > 0: the matrix has X more rows behind the R that compete; the sigmoids of their logits come back
+    as a third result, float32 [N, X]."""
     n, c = h.shape
-    r = w_router.shape[0]
-    if w_router.dtype != torch.float32 or correction.dtype != torch.float32 or w_router.shape[1] != c or correction.numel() != r:
-        raise ValueError("moe_route takes a float32 router matrix [R, C] and correction [R]")
+    r = w_router.shape[0] - int(extra)
+    if scoring not in ("softmax", "sigmoid"):
+        raise ValueError(f"unknown scoring {scoring!r}")
+    if (w_router.dtype != torch.float32 or w_router.shape[1] != c or r < 1
+            or (correction is not None and (correction.dtype != torch.float32 or correction.numel() != r))):
+        raise ValueError("moe_route takes a float32 router matrix [R + extra, C] and correction [R] (or none)")
     hp, ldh = _rows(h, "h")
     chosen = torch.empty((n, top), dtype=torch.int32, device=h.device)
     weights = torch.empty((n, top), dtype=torch.float32, device=h.device)
+    extras = torch.empty((n, int(extra)), dtype=torch.float32, device=h.device) if extra else None
     _check(_fn("moe", "akas_moe_route")(hp, ldh, _ptr(_dense(w_router, "w_router")), _ptr(correction), _ptr(chosen),
-                                       _ptr(weights), n, c, r, int(groups), int(keep), int(top), _code(h), _stream()),
+                                       _ptr(weights), n, c, r, int(groups), int(keep), int(top), _code(h),
+                                       int(scoring == "sigmoid"), int(bool(renormalize)), int(extra), _ptr(extras), _stream()),
            "moe_route")
-    return chosen, weights
+    return (chosen, weights, extras) if extra else (chosen, weights)
 
 
 # Which kernels run the experts in bfloat16: "auto" (default), the grouped product on the tensor cores
@@ -1654,7 +1693,21 @@ def _update_args(update, n, c):
     return _ptr(x), _ptr(a), _ptr(scale_a), _ptr(scale_b), float(mult)
 
 
-def _moe_experts_grouped(h, w_gate_up, w_down, chosen, weights, update=None):
+def _shared_args(shared, n, c):
+    """(y, gate, gate's pitch) of a dense result that the experts' last kernel adds (null pointers for none)."""
+    if shared is None:
+        return None, None, 0
+    y, gate = shared
+    if y.dtype != torch.float32 or y.shape != (n, c) or not y.is_contiguous():
+        raise ValueError("a shared expert's result is a dense float32 tensor [N, C]")
+    if gate is None:
+        return _ptr(y), None, 0
+    if gate.dtype != torch.float32 or gate.shape[0] != n:
+        raise ValueError("a shared expert's gate is float32, one number per token")
+    return _ptr(y), _ptr(gate), gate.stride(0)
+
+
+def _moe_experts_grouped(h, w_gate_up, w_down, chosen, weights, update=None, weight_input=False, shared=None):
     n, c = h.shape
     experts, f2, _ = w_gate_up.shape
     f, top = f2 // 2, chosen.shape[1]
@@ -1669,20 +1722,24 @@ def _moe_experts_grouped(h, w_gate_up, w_down, chosen, weights, update=None):
     y = torch.empty((cap, c), dtype=torch.float32, device=dev)
     out = torch.empty((n, c), dtype=torch.float32, device=dev) if update is None else update[0]
     _check(_fn("moe_grouped", "akas_moe_sort")(hp, ldh, _ptr(chosen), _ptr(row_of_pair), _ptr(tile_expert), _ptr(plan), _ptr(rows),
-                                              n, top, c, experts, _stream()), "moe_sort", kernels=2)
+                                              n, top, c, experts, _ptr(weights) if weight_input else None, _stream()),
+           "moe_sort", kernels=2)
     gemm = _fn("moe_grouped", "akas_moe_grouped_gemm")
     _check(gemm(_ptr(rows), _ptr(w_gate_up), _ptr(act), _ptr(tile_expert), _ptr(plan), cap, experts, f2, c, 2, _stream()),
            "grouped gate and up product")
     _check(gemm(_ptr(act), _ptr(w_down), _ptr(y), _ptr(tile_expert), _ptr(plan), cap, experts, c, f, 1, _stream()),
            "grouped down product")
-    _check(_fn("moe_grouped", "akas_moe_combine")(hp, ldh, _ptr(y), _ptr(row_of_pair), _ptr(weights), _ptr(out), n, top, c,
-                                                 *_update_args(update, n, c), _stream()), "moe_combine")
+    _check(_fn("moe_grouped", "akas_moe_combine")(hp, ldh, _ptr(y), _ptr(row_of_pair), None if weight_input else _ptr(weights),
+                                                 _ptr(out), n, top, c, *_update_args(update, n, c), *_shared_args(shared, n, c),
+                                                 _stream()), "moe_combine")
     return out
 
 
 @_flushes
-def moe_experts(h, w_gate_up, w_down, chosen, weights, update=None):
-    """The weighted sum of the chosen experts' results, float32 [N, C]. With ``update`` = (x, a, scale_a, scale_b, mult)
+def moe_experts(h, w_gate_up, w_down, chosen, weights, update=None, weight_input=False, shared=None):
+    """``weight_input``: the weight multiplies the expert's input, sum_k expert(w_k h), where otherwise it multiplies the
+    result. ``shared`` = (y float32 [N, C], gate float32 [N, 1] or None): y times its gate is added to the sum.
+    The weighted sum of the chosen experts' results, float32 [N, C]. With ``update`` = (x, a, scale_a, scale_b, mult)
     the sum is not returned but added into the residual stream by the last kernel: x += mult * (scale_a * a + scale_b *
     sum), in place; returns x."""
     n, c = h.shape
@@ -1694,13 +1751,14 @@ def moe_experts(h, w_gate_up, w_down, chosen, weights, update=None):
     if (moe_kernels == "auto" and h.dtype == torch.bfloat16 and n * top > _MOE_SIMPLE_PAIRS and ldh % 8 == 0 and hp % 16 == 0
             and _fn("moe_grouped", "akas_moe_grouped_takes")(c, f, experts)):
         _dense(w_gate_up, "w_gate_up"), _dense(w_down, "w_down")
-        return _moe_experts_grouped(h, w_gate_up, w_down, chosen, weights, update)
+        return _moe_experts_grouped(h, w_gate_up, w_down, chosen, weights, update, weight_input, shared)
     act = torch.empty((n * top, f), dtype=h.dtype, device=h.device)
     out = torch.empty((n, c), dtype=torch.float32, device=h.device) if update is None else update[0]
     _check(_fn("moe", "akas_moe_gate_up")(hp, ldh, _ptr(_dense(w_gate_up, "w_gate_up")), _ptr(chosen), _ptr(act), n, top, c, f,
-                                         experts, _code(h), _stream()), "moe_gate_up")
-    _check(_fn("moe", "akas_moe_down")(hp, ldh, _ptr(_dense(w_down, "w_down")), _ptr(chosen), _ptr(weights), _ptr(act),
-                                      _ptr(out), n, top, c, f, experts, _code(h), *_update_args(update, n, c), _stream()), "moe_down")
+                                         experts, _code(h), _ptr(weights) if weight_input else None, _stream()), "moe_gate_up")
+    _check(_fn("moe", "akas_moe_down")(hp, ldh, _ptr(_dense(w_down, "w_down")), _ptr(chosen), None if weight_input else _ptr(weights),
+                                      _ptr(act), _ptr(out), n, top, c, f, experts, _code(h), *_update_args(update, n, c),
+                                      *_shared_args(shared, n, c), _stream()), "moe_down")
     return out
 
 

@@ -145,20 +145,24 @@ def expert(h, w, p):
     return (silu(h @ w[p + "gate"].T) * (h @ w[p + "up"].T)) @ w[p + "down"].T
 
 
-def route(h, w, p, r):
-    """The chosen experts [T, top] and their weights: the largest of sigmoid(W_router h), as they are."""
+def route(h, w, p, r, margins=None):
+    """The chosen experts [T, top] and their weights: the largest of sigmoid(W_router h), as they are. ``margins``, a
+    list, receives per token the gap between the last score that was chosen and the first that was not."""
     s = torch.sigmoid(h @ w[p + "router"].T)
     weights, chosen = torch.topk(s, r["top"], dim=-1)
+    if margins is not None:
+        ordered = torch.sort(s, dim=-1, descending=True).values
+        margins.append((ordered[:, r["top"] - 1] - ordered[:, r["top"]]).tolist() if r["top"] < s.shape[1] else [1.0] * h.shape[0])
     return chosen, weights
 
 
-def feed_forward(h, w, p, mlp):
+def feed_forward(h, w, p, mlp, margins=None):
     """``dense``: W_down relu(W_up h)^2. ``moe``: every token's chosen experts run on the token's row times the
     expert's weight, and their results are summed; an expert that every token passes is added, times
     sigmoid(W_sg h), one number a token."""
     if mlp["kind"] == "dense":
         return torch.relu(h @ w[p + "up"].T) ** 2 @ w[p + "down"].T
-    chosen, weights = route(h, w, p, mlp["router"])
+    chosen, weights = route(h, w, p, mlp["router"], margins)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, g in zip(chosen[t].tolist(), weights[t]):
@@ -181,8 +185,9 @@ def run_order(cfg):
     return order + [(i, False) for i in range(loop["stop"], n)]
 
 
-def forward(tokens, w, cfg, trace=None):
-    """Logits [T, vocab] of one sequence; ``trace``, a list, receives the residual stream after every layer run."""
+def forward(tokens, w, cfg, trace=None, margins=None):
+    """Logits [T, vocab] of one sequence; ``trace``, a list, receives the residual stream after every layer run;
+    ``margins``, a list, one list per routed layer run of the tokens' routing margins (see ``route``)."""
     w = {k: v.to(F) for k, v in w.items()}
     eps = cfg["norm"]["eps"]
     first = w["embed"][torch.as_tensor(tokens)]
@@ -201,7 +206,7 @@ def forward(tokens, w, cfg, trace=None):
             y = latent_attention(h, w, p + "mix.", m, eps)
         x = x + dyt(y, w, p + "norm1b")
         if entry.get("mlp") is not None:
-            x = x + dyt(feed_forward(dyt(x, w, p + "norm2"), w, p + "mlp.", entry["mlp"]), w, p + "norm2b")
+            x = x + dyt(feed_forward(dyt(x, w, p + "norm2"), w, p + "mlp.", entry["mlp"], margins), w, p + "norm2b")
         if trace is not None:
             trace.append(x.clone())
     return dyt(x, w, "final.norm") @ w["embed"].T * cfg.get("logit_scale", 1.0)
