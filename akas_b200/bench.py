@@ -499,6 +499,30 @@ def penopel_shape_config(name: str) -> dict:
                 logit_softcap=30.0, layers=layers)
 
 
+# Kidarax at LFM2's layer sizes: the same width and vocabulary; fourteen layers of which two run twice (a loop), so sixteen
+# layer runs like LFM2's. The mixers take turns: retention (a head per 128 channels of the width, keys of 64 and values
+# of 128), latent attention (a head per 128 channels, 64 plain and 32 rotated channels, a latent of 96: a cached row of
+# 128 numbers) and biased attention with LFM2's head counts and a gate per channel. Feed-forwards take turns too: a dense
+# one without a gate, half again as wide as LFM2's gated one (as many parameters), and sixteen experts of a quarter of
+# LFM2's width of which a token passes three, beside one more that every token passes.
+def kidarax_shape_config(name: str) -> dict:
+    lfm2 = config_from_shape(name)
+    c, ff3 = lfm2.hidden_size, lfm2.feed_forward_size
+    heads = c // 128
+    retention = dict(heads=heads, dim=64, vdim=128, decay=[1.0 - 2.0 ** -(4 + 6 * i / max(1, heads - 1)) for i in range(heads)])
+    attention = dict(heads=lfm2.num_attention_heads, kv_heads=lfm2.num_key_value_heads, dim=lfm2.head_dim, vdim=lfm2.head_dim,
+                     scale=lfm2.head_dim ** -0.5, rot=dict(base=500000.0, dims=lfm2.head_dim, scaling=dict(factor=8.0)))
+    latent = dict(heads=heads, dim=64, rot_dim=32, vdim=64, kv_rank=96, scale=96 ** -0.5,
+                  rot=dict(base=1000000.0, dims=32, scaling=dict(factor=8.0, original=4096, fast=32.0, slow=1.0)))
+    dense = dict(kind="dense", ff=ff3 * 3 // 2)
+    moe = dict(kind="moe", expert=dict(ff=ff3 // 4), router=dict(experts=16, top=3), shared=dict(ff=ff3 // 4))
+    mixers = (("retention", retention), ("latent_attention", latent), ("attention", attention))
+    runs = len(lfm2.layer_kinds)
+    layers = [dict(type=mixers[i % 3][0], mixer=mixers[i % 3][1], mlp=moe if i % 2 else dense) for i in range(runs - 2)]
+    return dict(architecture="Kidarax", width=c, vocab=lfm2.vocab_size, norm=dict(eps=1e-5), logit_scale=float(c) ** -0.5,
+                loop=dict(start=runs // 2 - 2, stop=runs // 2, times=2), layers=layers)
+
+
 def config_from_shape(name: str):
     from .config import config_from_dict
 
@@ -525,7 +549,7 @@ def compare_designs(shape: str = "1.2b", prompt: int = 2048, batches=(8, 64), st
 
     rows = []
     shapes = {"lfm2": shape_config, "gigusun": gigusun_shape_config, "girelix": girelix_shape_config,
-              "penopel": penopel_shape_config}
+              "penopel": penopel_shape_config, "kidarax": kidarax_shape_config}
     for design, data in ((name, shapes[name](shape)) for name in designs):
         say(f"{design} {shape}: writing random weights")
         model_config = config_from_dict(data)

@@ -107,6 +107,18 @@ __device__ __forceinline__ float gate_activation_fast(float g, int act) {
   return __fdividef(g, 1.f + __expf(-y));
 }
 
+// An activation without a gate in the bfloat16 read-out of a product, y = act(product): 0 none, 1 the tanh form of
+// gelu, 2 the square of max(x, 0), 3 silu. (Fast division and exponential: the result is rounded to bfloat16 right after.)
+#define AKAS_PLAIN_NONE 0
+#define AKAS_PLAIN_GELU_TANH 1
+#define AKAS_PLAIN_RELU2 2
+#define AKAS_PLAIN_SILU 3
+__device__ __forceinline__ float plain_activation_fast(float x, int act) {
+  if (act == AKAS_PLAIN_RELU2) { const float r = fmaxf(x, 0.f); return r * r; }
+  if (act == AKAS_PLAIN_NONE) return x;
+  return gate_activation_fast(x, act == AKAS_PLAIN_GELU_TANH ? AKAS_ACT_GELU_TANH : AKAS_ACT_SILU);
+}
+
 // tanh(x) = 1 - 2 / (e^(2x) + 1) from the special-function unit: an absolute error of a few 1e-7, for results that are
 // rounded to bfloat16 next.
 __device__ __forceinline__ float tanh_fast(float x) {

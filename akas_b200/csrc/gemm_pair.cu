@@ -299,6 +299,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           float v[32], u[32];
           tmem_load32(taddr + c, v);
           tmem_load32(taddr + c + 32, u);
+          if (act != AKAS_PLAIN_NONE) {  // an activation without a gate on the product itself
+#pragma unroll
+            for (int i = 0; i < 32; ++i) { v[i] = plain_activation_fast(v[i], act); u[i] = plain_activation_fast(u[i], act); }
+          }
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
             uint4 o, p;
@@ -516,9 +520,11 @@ static int pair_dispatch(const void* x, const void* w, void* y, int M, int N, in
   if (epilogue == EPI_SWIGLU && (N % 2 || (N / 2) % 8)) return (int)cudaErrorInvalidValue;
   if (epilogue == EPI_BF16 && (N % 8 || bias != nullptr)) return (int)cudaErrorInvalidValue;
   if ((epilogue == EPI_ACC || epilogue == EPI_F32) && N % 4) return (int)cudaErrorInvalidValue;
-  if (act != AKAS_ACT_SILU && act != AKAS_ACT_GELU_TANH) return (int)cudaErrorInvalidValue;
+  // (read-out 0 takes an activation without a gate, AKAS_PLAIN_*; read-out 2 the gate's, AKAS_ACT_*)
+  if (epilogue == EPI_BF16 ? (act < AKAS_PLAIN_NONE || act > AKAS_PLAIN_SILU) : (act != AKAS_ACT_SILU && act != AKAS_ACT_GELU_TANH))
+    return (int)cudaErrorInvalidValue;
   switch (epilogue) {
-    case EPI_BF16: return launch_width<EPI_BF16>(x, w, y, M, N, K, nullptr, 0, stream);
+    case EPI_BF16: return launch_width<EPI_BF16>(x, w, y, M, N, K, nullptr, act, stream);
     case EPI_ACC: return launch_width<EPI_ACC>(x, w, y, M, N, K, bias, 0, stream);
     case EPI_SWIGLU: return launch_width<EPI_SWIGLU>(x, w, y, M, N, K, bias, act, stream);
     case EPI_F32: return launch_width<EPI_F32>(x, w, y, M, N, K, bias, 0, stream);
@@ -532,7 +538,8 @@ AKAS_API int akas_gemm_pair(const void* x, const void* w, void* y, int M, int N,
 
 // The same with a float32 bias: one number per output channel for the float32 read-outs (1: y += product + bias), or,
 // for read-out 2, [2F] (the gate rows' biases, then the up rows') and the gate's activation (0 silu, 1 the tanh form of
-// gelu): y = act(gate + b_g) * (up + b_u).
+// gelu): y = act(gate + b_g) * (up + b_u). Read-out 0 takes no bias but an activation without a gate (0 none, 1 the tanh
+// form of gelu, 2 the square of max(x, 0), 3 silu): y = act(product).
 AKAS_API int akas_gemm_pair_bias(const void* x, const void* w, void* y, int M, int N, int K, int epilogue, const float* bias,
                                  int act, cudaStream_t stream) {
   return pair_dispatch(x, w, y, M, N, K, epilogue, bias, act, stream);

@@ -159,7 +159,7 @@ struct Shape {
   int parts;          // blocks of a cluster that share a tile, one part of K each (1: no cluster)
   int part_blocks;    // 64-wide steps of K in a part (a multiple of G)
   const float* bias;  // float32, or null: one number per output channel (float32 read-outs), or [2F] for the gated read-out
-  int act;            // the gated read-out's activation: 0 silu, 1 the tanh form of gelu
+  int act;            // the gated read-out's activation: 0 silu, 1 the tanh form of gelu; the bfloat16 read-out's: AKAS_PLAIN_*
 };
 
 template <int EPI>
@@ -467,6 +467,9 @@ gemm_rows_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
               }
 #pragma unroll
               for (int i = 0; i < 16; ++i) v[i] = gate_activation_fast(v[i], sh.act) * u[i];  // the fast division: IEEE division cost more than the tile's loads
+            } else if (sh.act != AKAS_PLAIN_NONE) {  // an activation without a gate on the product itself
+#pragma unroll
+              for (int i = 0; i < 16; ++i) v[i] = plain_activation_fast(v[i], sh.act);
             }
             // row `lane` of 32 bytes, its two 16-byte units XORed with bit 7 of the address (the 32-byte swizzle)
 #pragma unroll
@@ -808,10 +811,12 @@ AKAS_API int akas_gemm_rows(const void* x, const void* w, void* y, int M, int O,
 
 // The same with a float32 bias: one number per output channel for the float32 read-outs (1: y += product + bias), or,
 // for read-out 2, [2F] (the gate rows' biases, then the up rows') and the gate's activation (0 silu, 1 the tanh form of
-// gelu): y = act(gate + b_g) * (up + b_u).
+// gelu): y = act(gate + b_g) * (up + b_u). Read-out 0 takes no bias but an activation without a gate (0 none, 1 the tanh
+// form of gelu, 2 the square of max(x, 0), 3 silu): y = act(product).
 AKAS_API int akas_gemm_rows_bias(const void* x, const void* w, void* y, int M, int O, int K, int epilogue, const float* bias,
                                  int act, cudaStream_t stream) {
-  if (act != AKAS_ACT_SILU && act != AKAS_ACT_GELU_TANH) return (int)cudaErrorInvalidValue;
+  if (epilogue == EPI_BF16 ? (act < AKAS_PLAIN_NONE || act > AKAS_PLAIN_SILU) : (act != AKAS_ACT_SILU && act != AKAS_ACT_GELU_TANH))
+    return (int)cudaErrorInvalidValue;
   if (epilogue == EPI_BF16 && bias != nullptr) return (int)cudaErrorInvalidValue;
   t_bias = bias;
   t_act = act;

@@ -82,7 +82,7 @@ struct ConvTail {
   float* state;             // [slots, L - 1, C]
   const int* seq_of_token;  // [M]: the request of a token, or -1 for padding
   const int* slots;         // [requests]: the state row of a request
-  int L, write;             // (gated read-out: L is the activation, 0 silu, 1 the tanh form of gelu)
+  int L, write;             // (gated read-out: L is the activation, 0 silu, 1 the tanh form of gelu; bfloat16 read-out: AKAS_PLAIN_*)
   // read-outs without a convolution: `bias` is one float32 per output channel (float32 read-outs: y = product + bias,
   // or += for the accumulating one), or [2F] for the gated read-out (the gate rows' biases, then the up rows')
   const float* in_shift;    // in_mode 2: the norm's shift [K]
@@ -519,7 +519,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
           if (o >= O) continue;
           const size_t at = (size_t)m * O + o;
           if (OUT != OUT_BF16 && tail.bias != nullptr) v += tail.bias[o];
-          if (OUT == OUT_BF16) ((bf16*)y_)[at] = __float2bfloat16_rn(v);
+          if (OUT == OUT_BF16) ((bf16*)y_)[at] = __float2bfloat16_rn(plain_activation_fast(v, tail.L));
           else if (OUT == OUT_F32) ((float*)y_)[at] = v;
           else ((float*)y_)[at] = before + v;
         }
@@ -576,7 +576,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap map_w, const void* __rest
             if (IN == IN_NORM) v *= 1.f / sqrtf(ss / (float)K + eps);
             const size_t at = (size_t)m * O + o;
             if (OUT != OUT_BF16 && tail.bias != nullptr) v += tail.bias[o];
-            if (OUT == OUT_BF16) ((bf16*)y_)[at] = __float2bfloat16_rn(v);
+            if (OUT == OUT_BF16) ((bf16*)y_)[at] = __float2bfloat16_rn(plain_activation_fast(v, tail.L));
             else if (OUT == OUT_F32) ((float*)y_)[at] = v;
             else ((float*)y_)[at] = before[n] + v;
           }
@@ -829,12 +829,14 @@ AKAS_API int akas_skinny_gemm(const void* x, const int* rows, const float* norm_
 // The same with more: in_mode 2, the input rows through a norm without sums, bf16(tanh(alpha x) * norm_w + shift), in
 // front of out modes 0, 1 and 3; a float32 bias on the float32 read-outs (one number per output channel: y = product +
 // bias, or += for the accumulating one) or on the gated read-out ([2F], with `act` 0 silu or 1 the tanh form of gelu:
-// y = act(gate + b_g) * (up + b_u)).
+// y = act(gate + b_g) * (up + b_u)). Out mode 0 takes no bias but an activation without a gate (`act` 0 none, 1 the tanh
+// form of gelu, 2 the square of max(x, 0), 3 silu): y = act(product).
 AKAS_API int akas_skinny_gemm_more(const void* x, const int* rows, const float* norm_w, const float* shift, const float* alpha,
                                    const void* W, void* y, int M, int O, int K, int in_mode, int out_mode, const float* bias,
                                    int act, cudaStream_t stream) {
   if (out_mode < OUT_BF16 || out_mode > OUT_SWIGLU || in_mode == IN_NORM) return (int)cudaErrorInvalidValue;
-  if (act != AKAS_ACT_SILU && act != AKAS_ACT_GELU_TANH) return (int)cudaErrorInvalidValue;
+  if (out_mode == OUT_BF16 ? (act < AKAS_PLAIN_NONE || act > AKAS_PLAIN_SILU) : (act != AKAS_ACT_SILU && act != AKAS_ACT_GELU_TANH))
+    return (int)cudaErrorInvalidValue;
   if (out_mode == OUT_BF16 && bias != nullptr) return (int)cudaErrorInvalidValue;
   const ConvTail tail{nullptr, bias, nullptr, nullptr, nullptr, act, 0, shift, alpha};
   return skinny_dispatch(x, rows, norm_w, 0.f, 0, W, y, M, O, K, in_mode, out_mode, tail, stream);

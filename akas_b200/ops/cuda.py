@@ -639,6 +639,60 @@ def linear_gated(x, w_gate_up, width, bias, activation):
     return out
 
 
+_READOUT_PLAIN = {"gelu_tanh": 1, "relu2": 2, "silu": 3}  # the bfloat16 read-outs' activations without a gate (0: none)
+
+
+def linear_activated(x, w, activation):
+    """act(x . w^T) in x's dtype, for an activation without a gate ("relu2", "gelu_tanh", "silu"). In bfloat16 the
+    activation rides in the product's read-out on the float32 sums; None where no kernel with that read-out takes the
+    sizes (the caller then runs the product in float32 and ``activation``)."""
+    n, k = x.shape
+    o = w.shape[0]
+    if activation not in _READOUT_PLAIN:
+        raise ValueError(f"unknown activation {activation!r}")
+    if (w.shape[1] != k or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or _chain_open or decode_products != "skinny"
+            or products == "library"):
+        return None
+    _dense(x, "x"), _dense(w, "w")
+    if _skinny_fits(n, k):
+        route = "skinny"
+    elif k % 8 or o % 8:
+        return None
+    elif _rows_takes(n, o, k, 0):
+        route = "rows"
+    elif n > _SKINNY_ROWS:
+        route = "paired"
+    else:
+        return None
+    out = torch.empty((n, o), dtype=torch.bfloat16, device=x.device)
+    act = _READOUT_PLAIN[activation]
+    if route == "skinny":
+        _check(_fn("skinny_gemm", "akas_skinny_gemm_more")(_ptr(x), None, None, None, None, _ptr(w), _ptr(out), n, o, k, 0,
+                                                          _OUT_BF16, None, act, _stream()), "skinny product with an activation")
+    else:
+        name = "gemm_rows" if route == "rows" else "gemm_pair"
+        _check(_fn(name, f"akas_{name}_bias")(_ptr(x), _ptr(w), _ptr(out), n, o, k, 0, None, act, _stream()),
+               f"{name} product with an activation")
+    return out
+
+
+def dyt_linear_activated(h, alpha, weight, shift, w, activation, rows=None):
+    """act(linear(dynamic_tanh(h[rows]), w)) for few tokens: the norm on the product's way in, the activation in its
+    read-out. None where the fused kernel does not take the sizes or the dtype."""
+    m = rows.numel() if rows is not None else h.shape[0]
+    k, o = h.shape[1], w.shape[0]
+    if activation not in _READOUT_PLAIN:
+        raise ValueError(f"unknown activation {activation!r}")
+    if (w.dtype != torch.bfloat16 or h.dtype != torch.float32 or not h.is_contiguous() or w.shape[1] != k or _chain_open
+            or decode_products != "skinny" or not _skinny_fits(m, k) or alpha.dtype != torch.float32):
+        return None
+    out = torch.empty((m, o), dtype=torch.bfloat16, device=h.device)
+    _check(_fn("skinny_gemm", "akas_skinny_gemm_more")(_ptr(h), _ptr(rows), _ptr(weight), _ptr(shift), _ptr(alpha), _ptr(_dense(w, "w")),
+                                                      _ptr(out), m, o, k, 2, _OUT_BF16, None, _READOUT_PLAIN[activation], _stream()),
+           "skinny product behind a norm without sums, with an activation")
+    return out
+
+
 def dyt_linear(h, alpha, weight, shift, w, out_dtype=None, rows=None, gated=None):
     """linear(dynamic_tanh(h[rows]), w) for few tokens, the norm computed on the product's way in; with ``gated`` =
     (width, bias or None, activation) through the gated read-out as ``linear_gated``. None where the fused kernel does not take

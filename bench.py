@@ -2,8 +2,8 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--dtype bfloat16|float32]
     python bench.py --impl reference        (prints why the reference cannot run here)
-    python bench.py --compare gigusun|girelix|penopel [--shape 1.2b|700m|350m]
-                                            (Gigusun beside LFM2, Girelix or Penopel beside Gigusun, at equal layer sizes: prefill,
+    python bench.py --compare gigusun|girelix|penopel|kidarax [--shape 1.2b|700m|350m]
+                                            (Gigusun beside LFM2, Girelix or Penopel beside Gigusun, Kidarax beside Girelix, at equal layer sizes: prefill,
                                              decode, time per operation;
                                              AKAS_B200_BENCH_WATCHDOG=seconds prints every thread's stack to stderr at
                                              that interval, so that a run that stalls says where)
@@ -134,9 +134,9 @@ def main():
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers than the configuration has (named in config)")
     ap.add_argument("--dtype", default="bfloat16", choices=("bfloat16", "float32"))
     ap.add_argument("--skip-points", action="store_true", help="leave out decode at batches 1 and 64")
-    ap.add_argument("--compare", choices=("gigusun", "girelix", "penopel"), default=None,
+    ap.add_argument("--compare", choices=("gigusun", "girelix", "penopel", "kidarax"), default=None,
                     help="instead of the default workload: this design beside its closest neighbour (gigusun: LFM2; girelix and "
-                         "penopel: Gigusun) "
+                         "penopel: Gigusun; kidarax: Girelix) "
                          "at equal layer sizes, one JSON line each")
     ap.add_argument("--shape", default="1.2b", help="layer sizes of --compare: 350m, 700m, 1.2b, or several with commas")
     args = ap.parse_args()
@@ -152,7 +152,8 @@ def main():
             faulthandler.dump_traceback_later(watchdog, repeat=True)
 
         for shape in args.shape.split(","):
-            designs = ("lfm2", "gigusun") if args.compare == "gigusun" else ("gigusun", args.compare)
+            neighbour = {"gigusun": "lfm2", "kidarax": "girelix"}.get(args.compare, "gigusun")
+            designs = (neighbour, args.compare)
             for row in compare_designs(shape, steps=min(args.steps, 64), warmup=max(3, min(args.warmup, 8)), designs=designs):
                 row["peaks"] = peaks()
                 print(json.dumps(row), flush=True)

@@ -732,3 +732,36 @@ def test_a_cached_row_without_a_query_latent(dtype):
         out = ops.latent_norm_store(proj, 0, kv_rank, rot, None, kw, 1e-5, cos, sin, False, pool, table, seq, pos, page)
         assert out.shape == (n, 0)
     _close(pools[1], pools[0], 1e-6 if dtype == torch.float32 else 8e-3, "the cached rows")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("activation", ["relu2", "gelu_tanh", "silu"])
+@pytest.mark.parametrize("n,k,o", [(3, 64, 48), (16, 192, 320), (9, 2048, 48), (1, 128, 1008), (40, 264, 528), (128, 2048, 320),
+                                   (300, 192, 256), (700, 512, 1536), (20, 100, 40), (33, 64, 20)])
+def test_products_with_an_activation_in_the_read_out(n, k, o, activation):
+    """The three product kernels' bfloat16 read-out with an activation on the float32 sums, and the fused norm in
+    front of it for few tokens, against the product in float32 followed by the activation's own kernel's statement."""
+    from akas_b200.ops import cuda, reference
+
+    cuda.require(cuda.libraries_for(torch.bfloat16, ()))
+    g = torch.Generator().manual_seed(n * 7 + o)
+    x = torch.randn(n, k, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(o, k, generator=g) * k ** -0.5).to(torch.bfloat16).cuda()
+    want = reference.activation(reference.linear(x, w, out_dtype=torch.float32), activation, torch.bfloat16)
+    got = cuda.linear_activated(x, w, activation)
+    if got is None:  # sizes that no fused read-out takes: the part's other way
+        assert k % 8 or o % 8
+        got = cuda.activation(cuda.linear(x, w, out_dtype=torch.float32), activation, torch.bfloat16)
+    _close(got, want, 1.2e-2, f"{activation} in the read-out")
+    for status in (cuda.skinny_status, cuda.gemm_rows_status, cuda.gemm_pair_status):
+        assert status() == 0
+    if n <= 16 and k % 64 == 0:
+        h = (torch.randn(n + 2, k, generator=g) * 2).cuda()
+        rows = torch.arange(n, dtype=torch.int32).cuda() + 1
+        alpha = torch.tensor(0.8).cuda()
+        nw, nb = torch.randn(k, generator=g).cuda(), torch.randn(k, generator=g).cuda() * 0.2
+        fused = cuda.dyt_linear_activated(h, alpha, nw, nb, w, activation, rows)
+        assert fused is not None
+        normed = reference.dynamic_tanh(h, alpha, nw, nb, torch.bfloat16, rows)
+        _close(fused, reference.activation(reference.linear(normed, w, out_dtype=torch.float32), activation, torch.bfloat16), 1.5e-2,
+               "norm, product and activation")
