@@ -105,3 +105,29 @@ def test_generate_runs_a_penopel_folder(tmp_path, capsys):
     for extra in ([], ["--temperature", "0.7", "--top-k", "20", "--seed", "2", "--dtype", "float32"]):
         main(["generate", "--model", str(tmp_path / "p"), "--prompt", "5 17 3 9", "--max-tokens", "7", "--ignore-eos", *extra])
         assert len(capsys.readouterr().out.split()) == 7
+
+
+def test_random_and_inspect_take_a_kidarax_configuration(tmp_path, capsys):
+    import tiny_kidarax
+
+    config = tiny_kidarax.CONFIGS["mix"]
+    main(["random", "--out", str(tmp_path / "k"), "--config", json.dumps(config), "--seed", "4"])
+    capsys.readouterr()
+    main(["inspect", "--model", str(tmp_path / "k")])
+    report = json.loads(capsys.readouterr().out)
+    assert report["architecture"] == "Kidarax" and report["config"] == json.loads(json.dumps(config))
+    assert {"l0.norm1b.alpha", "l0.norm2b.b", "l0.mlp.router", "l0.mlp.e5.down", "l0.mlp.shared.sg", "l1.mix.dkv.norm", "l1.mix.sink",
+            "l1.mlp.up", "l2.mix.k.b", "l2.mix.g", "final.norm.b"} <= set(report["inventory"])
+    # no weight for the retention's norm, no head of its own, no shared expert where the layer names none, no feed-forward norms without a feed-forward
+    assert not {"l0.mix.norm", "head", "l2.mlp.shared.gate", "l3.mlp.up"} & set(report["inventory"])
+
+
+@pytest.mark.gpu
+def test_generate_runs_a_kidarax_folder(tmp_path, capsys):
+    import tiny_kidarax
+
+    main(["random", "--out", str(tmp_path / "k"), "--config", json.dumps(tiny_kidarax.CONFIGS["mix"]), "--seed", "4"])
+    capsys.readouterr()
+    for extra in ([], ["--temperature", "0.7", "--top-k", "20", "--seed", "2", "--dtype", "float32"]):
+        main(["generate", "--model", str(tmp_path / "k"), "--prompt", "5 17 3 9", "--max-tokens", "7", "--ignore-eos", *extra])
+        assert len(capsys.readouterr().out.split()) == 7
