@@ -309,9 +309,13 @@ AKAS_API int akas_attention_general(const void* q, const void* k_pool, const voi
                                     int window, int keep_first, float cap, const float* r1, const float* r2, int sink,
                                     const void* gate, long long ldg, int page_size, int N, int H, int G, int D, int V,
                                     int dtype, const float* sinks, float out_scale, long long ldo, long long vpitch,
-                                    int gate_channels, cudaStream_t stream) {
+                                    int gate_channels, int gate_dtype, cudaStream_t stream) {
   if (N <= 0) return 0;
   if (G <= 0 || H % G || vpitch < V) return (int)cudaErrorInvalidValue;
+  if (dtype == AKAS_BF16 && gate != nullptr && gate_dtype == AKAS_F32)  // the gate's logits as a float32 product left them
+    return launch_general<bf16, float>(q, k_pool, v_pool, block_table, max_blocks, seq_of_token, positions, out, scale, window,
+                                       keep_first, cap, r1, r2, sink, gate, ldg, page_size, N, H, G, D, V, sinks, out_scale, ldo, vpitch, gate_channels, stream);
+  if (dtype == AKAS_F32 && gate != nullptr && gate_dtype != AKAS_F32) return (int)cudaErrorInvalidValue;
   if (dtype == AKAS_F32)
     return launch_general<float, float>(q, k_pool, v_pool, block_table, max_blocks, seq_of_token, positions, out, scale, window,
                                         keep_first, cap, r1, r2, sink, gate, ldg, page_size, N, H, G, D, V, sinks, out_scale, ldo, vpitch, gate_channels, stream);

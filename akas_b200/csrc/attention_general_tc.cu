@@ -47,17 +47,23 @@ struct Options {
   const float* r1;
   const float* r2;
   int window, keep_first, sink;
-  const bf16* gate;
+  const void* gate;    // logits of the output gate, bfloat16 or (gate_f32) float32, or null
   long long ldg;
   const float* sinks;  // a learned sink logit per head, or null
   float out_scale;
   long long ldo;       // elements between the output rows of two tokens
   long long vpitch;    // elements between two value rows in the pages (V, or more where a row holds more than the value)
   int gate_channels;   // the gate has one logit per output channel [H * V] of a token, not one per head [H]
+  int gate_f32;        // the gate's logits are float32 (the rows of a product that left float32)
 };
 
+__device__ __forceinline__ float gate_at(const Options& opt, size_t at) {  // sigmoid of the logit at an element offset
+  const float z = opt.gate_f32 ? reinterpret_cast<const float*>(opt.gate)[at] : to_f32(reinterpret_cast<const bf16*>(opt.gate)[at]);
+  return 1.f / (1.f + __expf(-z));
+}
+
 __device__ __forceinline__ float gate_of(const Options& opt, size_t token, int head, int V, int c) {
-  return 1.f / (1.f + __expf(-to_f32(opt.gate[token * opt.ldg + (size_t)head * V + c])));
+  return gate_at(opt, token * opt.ldg + (size_t)head * V + c);
 }
 
 constexpr int kTableBefore = 128, kTableAfter = 192;  // entries of the penalty table on either side of the window's distances
@@ -310,7 +316,7 @@ general_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_po
     float inv = l_run[h2] > 0.f ? 1.f / l_run[h2] : 0.f;
     const size_t token = packed ? q0 : q0 + row;
     const bool by_channel = opt.gate != nullptr && opt.gate_channels;
-    if (opt.gate != nullptr && !by_channel) inv *= 1.f / (1.f + __expf(-to_f32(opt.gate[token * opt.ldg + head2[h2]])));
+    if (opt.gate != nullptr && !by_channel) inv *= gate_at(opt, token * opt.ldg + head2[h2]);
     inv *= opt.out_scale;
     bf16* dst = out + token * opt.ldo + (size_t)head2[h2] * V;
 #pragma unroll
@@ -361,7 +367,7 @@ __global__ void general_merge_kernel(const float* __restrict__ partial, const in
     for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
     const float denom = part + (sunk ? exp2f(sink2 - top) : 0.f);
     float inv = denom > 0.f ? opt.out_scale / denom : 0.f;
-    if (opt.gate != nullptr && !opt.gate_channels) inv *= 1.f / (1.f + __expf(-to_f32(opt.gate[(size_t)token * opt.ldg + head])));
+    if (opt.gate != nullptr && !opt.gate_channels) inv *= gate_at(opt, (size_t)token * opt.ldg + head);
     if (lane == 0) inv_s = inv;
   }
   __syncthreads();
@@ -415,7 +421,7 @@ AKAS_API int akas_attention_general_tc(const void* q, const void* k_pool, const 
                                        int window, int keep_first, float cap, const float* r1, const float* r2, int sink,
                                        const void* gate, long long ldg, int page_size, int tiles, int H, int KH, int D, int V,
                                        int R, int packed, const float* sinks, float out_scale, long long ldo, float* partial,
-                                       int splits, long long vpitch, int gate_channels, cudaStream_t stream) {
+                                       int splits, long long vpitch, int gate_channels, int gate_dtype, cudaStream_t stream) {
   if (!akas_attention_general_tc_takes(D, V)) return 3999;
   if (ldo % 2 || vpitch % 8 || vpitch < V) return 3999;
   // parts: packed launches only; partial holds (first token of the launch + R) * H * splits * (V + 2) floats
@@ -423,7 +429,7 @@ AKAS_API int akas_attention_general_tc(const void* q, const void* k_pool, const 
   if (packed && (KH <= 0 || H / KH > BQ || tiles != R)) return 3999;
   if (KH <= 0 || H % KH || tiles > 65535 || R <= 0) return (int)cudaErrorInvalidValue;
   if (tiles <= 0) return 0;
-  const Options opt = {scale, cap, r1, r2, window, keep_first, sink, (const bf16*)gate, ldg, sinks, out_scale, ldo, vpitch, gate_channels};
+  const Options opt = {scale, cap, r1, r2, window, keep_first, sink, gate, ldg, sinks, out_scale, ldo, vpitch, gate_channels, gate_dtype == AKAS_F32};
   const int dk = (D + 31) / 32, dv = (V + 31) / 32;
 #define AKAS_TC(A, B)                                                                                                   \
   if (dk == A && dv == B)                                                                                               \

@@ -87,13 +87,13 @@ _SIGNATURES = {
                                c_void_p, c_void_p],
         "akas_attention_general": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_int,
                                    c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int,
-                                   c_int, c_int, c_int, c_void_p, c_float, c_longlong, c_longlong, c_int, c_void_p],
+                                   c_int, c_int, c_int, c_void_p, c_float, c_longlong, c_longlong, c_int, c_int, c_void_p],
     },
     "attention_general_tc": {
         "akas_attention_general_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float,
                                       c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_void_p, c_longlong, c_int, c_int,
                                       c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_longlong, c_void_p, c_int,
-                                      c_longlong, c_int, c_void_p],
+                                      c_longlong, c_int, c_int, c_void_p],
         "akas_attention_general_tc_takes": [c_int, c_int],
     },
     "moe_grouped": {
@@ -1535,14 +1535,15 @@ def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, s
         vd = vpitch = v_pool.shape[3]
     heads = q.shape[1] // d
     _dense(q, "q")
-    if q.dtype != k_pool.dtype or (gate is not None and gate.dtype != q.dtype):
-        raise TypeError("attention_general: q, the pages and the gate must have one dtype")
+    if q.dtype != k_pool.dtype or (gate is not None and gate.dtype not in (q.dtype, torch.float32)):
+        raise TypeError("attention_general: q and the pages must have one dtype, the gate theirs or float32")
     if sinks is not None and (sinks.dtype != torch.float32 or sinks.numel() != heads):
         raise ValueError("attention_general: sinks must be float32 [heads]")
     gp, ldg = _rows(gate, "gate") if gate is not None else (None, 0)
     if gate is not None and gate.shape != (n, heads * vd if gate_channels else heads):
         raise ValueError("attention_general: the gate is [N, heads], or with gate_channels [N, heads * value_dim]")
     channels = int(bool(gate_channels and gate is not None))
+    gate_code = _code(gate) if gate is not None else _code(q)
     if out is None:
         out = torch.empty((n, heads * vd), dtype=q.dtype, device=q.device)
     elif out.shape != (n, heads * vd) or out.dtype != q.dtype:
@@ -1573,13 +1574,13 @@ def attention_general(q, k_pool, v_pool, block_table, seq_of_token, positions, s
                 err = _fn("attention_general_tc", "akas_attention_general_tc")(
                     _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table[start:]), block_table.shape[1],
                     _ptr(ctx.cu_seqlens[start:]), _ptr(positions), op, *options, tiles, heads, kh, d, vd, requests,
-                    packed, *tail, _ptr(partial), splits, vpitch, channels, _stream())
+                    packed, *tail, _ptr(partial), splits, vpitch, channels, gate_code, _stream())
                 _check(err, "attention_general (tensor cores)")
             singles = 0
     if singles:
         _check(_fn("attention_general", "akas_attention_general")(
             _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token), _ptr(positions),
-            op, *options, singles, heads, kh, d, vd, _code(q), *tail, vpitch, channels, _stream()), "attention_general")
+            op, *options, singles, heads, kh, d, vd, _code(q), *tail, vpitch, channels, gate_code, _stream()), "attention_general")
     return out
 
 

@@ -187,8 +187,6 @@ class Attention(Mixer):
             more["out_scale"] = out_scale
         if s.gate == "channel":
             more["gate_channels"] = True
-        if gate is not None and gate.dtype != qn.dtype:
-            gate = gate.to(qn.dtype)  # (a float32 product, because of biases: the gate's logits in the pages' dtype)
         return ops.attention_general(
             qn, cache.k, cache.v, table, ctx.seq_of_token, ctx.positions, self.scale, s.window, s.keep_first,
             s.softcap, self.r1, self.r2, s.sink is True, gate, cache.page_size, ctx, **more,

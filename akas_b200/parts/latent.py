@@ -124,7 +124,7 @@ class LatentAttention(Mixer):
         head_gate = None
         if s.gate == "head":
             # one number per head commutes with the head's value product: it rides in attention's read-out
-            head_gate = proj[:, first : first + s.num_heads].to(q.dtype)
+            head_gate = proj[:, first : first + s.num_heads]  # (float32, as the product left them)
         latent = ops.attention_general(
             q, cache.kv, cache.kv, table, ctx.seq_of_token, ctx.positions, s.scale, s.window, 0, None, None, None,
             s.sink is True, head_gate, cache.page_size, ctx, values_in_keys=s.kv_rank, **more,

@@ -660,6 +660,13 @@ def test_a_gate_per_channel_in_the_general_attention(heads, kv_heads, dim, vdim,
     _close(plainly, want, tol, "a gate per channel, plain kernel")
     per_head = reference.attention_general(*args[:13], gate[:, :heads].contiguous(), page)
     assert (per_head.double() - want.double()).abs().max() > 1e-2
+    if dtype == torch.bfloat16:
+        # the gate's logits as a float32 product leaves them (rows that are parts of wider rows), per channel and per head
+        wide = torch.zeros(n, heads * vdim + 12, device="cuda")
+        wide[:, 4 : 4 + heads * vdim] = gate.float()
+        for ctx in (Ctx, None):
+            _close(cuda.attention_general(*args[:13], wide[:, 4 : 4 + heads * vdim], page, ctx, gate_channels=True), want, tol, "float32 logits")
+            _close(cuda.attention_general(*args[:13], wide[:, 4 : 4 + heads], page, ctx), per_head, tol, "float32 logits, a gate per head")
 
 
 @pytest.mark.gpu
