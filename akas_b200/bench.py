@@ -503,8 +503,8 @@ def penopel_shape_config(name: str) -> dict:
 # layer runs like LFM2's. The mixers take turns: retention (a head per 128 channels of the width, keys of 64 and values
 # of 128), latent attention (a head per 128 channels, 64 plain and 32 rotated channels, a latent of 96: a cached row of
 # 128 numbers) and biased attention with LFM2's head counts and a gate per channel. Feed-forwards take turns too: a dense
-# one without a gate, half again as wide as LFM2's gated one (as many parameters), and sixteen experts of a quarter of
-# LFM2's width of which a token passes three, beside one more that every token passes.
+# one without a gate, as wide as LFM2's gated one (four times the model's width at the 1.2b sizes), and sixteen experts of
+# a quarter of that width of which a token passes three, beside one more that every token passes.
 def kidarax_shape_config(name: str) -> dict:
     lfm2 = config_from_shape(name)
     c, ff3 = lfm2.hidden_size, lfm2.feed_forward_size
@@ -514,7 +514,7 @@ def kidarax_shape_config(name: str) -> dict:
                      scale=lfm2.head_dim ** -0.5, rot=dict(base=500000.0, dims=lfm2.head_dim, scaling=dict(factor=8.0)))
     latent = dict(heads=heads, dim=64, rot_dim=32, vdim=64, kv_rank=96, scale=96 ** -0.5,
                   rot=dict(base=1000000.0, dims=32, scaling=dict(factor=8.0, original=4096, fast=32.0, slow=1.0)))
-    dense = dict(kind="dense", ff=ff3 * 3 // 2)
+    dense = dict(kind="dense", ff=ff3)
     moe = dict(kind="moe", expert=dict(ff=ff3 // 4), router=dict(experts=16, top=3), shared=dict(ff=ff3 // 4))
     mixers = (("retention", retention), ("latent_attention", latent), ("attention", attention))
     runs = len(lfm2.layer_kinds)

@@ -63,7 +63,7 @@ def _rot(where: str, m: Mapping[str, Any], most: int, blended: bool) -> None:
         if not isinstance(scaling, Mapping):
             raise ConfigError(f"{w} must be an object")
         _number(w, scaling, "factor")
-        if blended:
+        if blended and any(key in scaling for key in ("original", "fast", "slow")):
             for key in ("original", "fast", "slow"):
                 _number(w, scaling, key)
             if base == 1.0:
@@ -79,7 +79,7 @@ def _rope(head: int, rot: Mapping[str, Any], dims: int, blended: bool) -> Option
     if s is None:
         return RopeSpec(head, float(rot["base"]), dims)
     factor = float(s["factor"])
-    if not blended:
+    if not blended or "original" not in s:  # (a scaling that names a factor only stretches evenly, whatever the mixer)
         return RopeSpec(head, float(rot["base"]), dims, linear_factor=factor)
     return RopeSpec(head, float(rot["base"]), dims, blend=(factor, float(s["original"]), float(s["fast"]), float(s["slow"])),
                     amplitude=0.1 * math.log(factor) + 1.0)
