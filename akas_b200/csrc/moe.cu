@@ -148,9 +148,12 @@ moe_route_kernel(const T* __restrict__ h, long long ldh, const float* __restrict
   for (int j = lane; j < extra; j += 32) extras[(size_t)n * extra + j] = 1.f / (1.f + expf(-zt[RC + j]));
   R = RC;  // from here on: the outputs that compete
   if (sigmoid) {
+    // Without a correction the choice goes by the logits themselves: the same order as their sigmoids', and two large
+    // logits whose sigmoids both round to one still compare.
     for (int e = lane; e < R; e += 32) {
-      zt[e] = 1.f / (1.f + expf(-zt[e]));
-      pt[e] = zt[e] + (correction != nullptr ? correction[e] : 0.f);
+      const float logit = zt[e];
+      zt[e] = 1.f / (1.f + expf(-logit));
+      pt[e] = correction != nullptr ? zt[e] + correction[e] : logit;
     }
   } else {
     float top_z = -INFINITY;

@@ -629,14 +629,18 @@ def moe_route(h, w_router, correction, groups, keep, top, scoring="softmax", ren
     score is their largest choice score, and only outputs of the ``keep`` best groups can be chosen; the ``top``
     largest choice scores win (ties: the lower index). Returns (chosen int32 [N, top], weights float32 [N, top]): the
     chosen outputs in the order of their choice scores and their plain scores over their sum (+ 1e-20).
-    ``scoring="sigmoid"``: a score is the sigmoid of its logit; ``correction`` None: none; ``renormalize`` False: the
+    ``scoring="sigmoid"``: a score is the sigmoid of its logit (without a correction the choice goes by the logits, which
+    order the same way); ``correction`` None: none; ``renormalize`` False: the
     weights are the chosen scores as they are. ``extra`` = X > 0: w_router has X more rows [R + X, C] that take no part
     in the choice; the sigmoids of their logits are returned as a third result, float32 [N, X]."""
     n = h.shape[0]
     r = w_router.shape[0] - extra
     z = h.to(torch.float32) @ w_router.to(torch.float32).T
     s = torch.softmax(z[:, :r], dim=-1) if scoring == "softmax" else torch.sigmoid(z[:, :r])
-    pick = s + correction.to(torch.float32) if correction is not None else s
+    if correction is not None:
+        pick = s + correction.to(torch.float32)
+    else:  # the logits order as their scores do, and still compare where two sigmoids round to one
+        pick = z[:, :r].clone() if scoring == "sigmoid" else s
     if groups > 1 and keep < groups:
         best = pick.reshape(n, groups, r // groups).max(dim=-1).values
         order = torch.argsort(best, dim=-1, descending=True, stable=True)

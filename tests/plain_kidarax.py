@@ -147,11 +147,12 @@ def expert(h, w, p):
 
 def route(h, w, p, r, margins=None):
     """The chosen experts [T, top] and their weights: the largest of sigmoid(W_router h), as they are. ``margins``, a
-    list, receives per token the gap between the last score that was chosen and the first that was not."""
-    s = torch.sigmoid(h @ w[p + "router"].T)
+    list, receives per token the gap between the last logit that was chosen and the first that was not."""
+    z = h @ w[p + "router"].T
+    s = torch.sigmoid(z)
     weights, chosen = torch.topk(s, r["top"], dim=-1)
     if margins is not None:
-        ordered = torch.sort(s, dim=-1, descending=True).values
+        ordered = torch.sort(z, dim=-1, descending=True).values
         margins.append((ordered[:, r["top"] - 1] - ordered[:, r["top"]]).tolist() if r["top"] < s.shape[1] else [1.0] * h.shape[0])
     return chosen, weights
 

@@ -93,10 +93,11 @@ LENGTHS = {"mix": [1, 45, 2, 97, 33, 130, 64], "odd": [70, 3, 41, 100], "ragged"
 TOL = {"float32": 3e-5, "bfloat16": 3e-2}  # largest |difference| over largest |reference logit|
 
 
-def make_folder(config, seed, folder, sharp=True):
-    """A model folder with random weights. ``sharp``: queries and keys large enough for peaked scores; always: sinks of
-    both signs and of the scores' size, norms with slopes of their own, shifts and biases that are not small, routers
-    whose scores spread over (0, 1)."""
+def make_folder(config, seed, folder, sharp=True, std=0.08):
+    """A model folder with random weights of deviation ``std`` (a wide model wants a smaller one, or every product
+    saturates the norm behind it). ``sharp``: queries and keys large enough for peaked scores; always: sinks of both
+    signs and of the scores' size, norms with slopes of their own, shifts and biases that are not small, routers whose
+    scores spread over (0, 1)."""
     from safetensors.torch import save_file
 
     from akas_b200.config import config_from_dict
@@ -104,7 +105,7 @@ def make_folder(config, seed, folder, sharp=True):
 
     folder = Path(folder)
     folder.mkdir(parents=True, exist_ok=True)
-    tensors = random_tensors(config_from_dict(config), seed=seed, std=0.08, dtype="float32")
+    tensors = random_tensors(config_from_dict(config), seed=seed, std=std, dtype="float32")
     g = torch.Generator().manual_seed(seed + 1)
     kinds = {f"l{i}.": entry["type"] for i, entry in enumerate(config["layers"])}
     for name in list(tensors):
@@ -116,7 +117,7 @@ def make_folder(config, seed, folder, sharp=True):
         if name.endswith("mix.sink"):
             tensors[name] = torch.randn(tensors[name].shape, generator=g) * 2.0
         if name.endswith(("mlp.router", "shared.sg")):
-            tensors[name] = tensors[name] * 6.0
+            tensors[name] = tensors[name] * (0.48 / std) * min(1.0, (64.0 / config["width"]) ** 0.5)  # logits of a few units at any width
         if name.endswith(".alpha"):
             tensors[name] = 0.3 + torch.rand(tensors[name].shape, generator=g)
         if name.endswith(".b"):
