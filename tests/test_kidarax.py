@@ -199,7 +199,7 @@ def test_rotary_rates_linear_and_blended():
         (dict(base=10000.0, dims=16), False),
         (dict(base=10000.0, dims=16, scaling=dict(factor=4.0)), False),
         (dict(base=300.0, dims=16, scaling=dict(factor=6.0, original=48, fast=8.0, slow=0.5)), True),
-        (dict(base=500000.0, dims=32, scaling=dict(factor=8.0, original=512, fast=32.0, slow=1.0)), True),
+        (dict(base=400000.0, dims=32, scaling=dict(factor=4.0, original=1024, fast=16.0, slow=2.0)), True),
         (dict(base=50.0, dims=6, scaling=dict(factor=3.0, original=4000, fast=2.0, slow=1.0)), True),   # every pair slowed or nearly
         (dict(base=1e6, dims=8, scaling=dict(factor=5.0, original=2, fast=64.0, slow=32.0)), True),     # lo = hi = 0: a step at pair 0
     ]
@@ -673,7 +673,7 @@ def test_a_gate_per_channel_in_the_general_attention(heads, kv_heads, dim, vdim,
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("experts,top,c,f,extra", [(6, 2, 80, 24, 1), (5, 1, 48, 16, 0), (3, 3, 52, 20, 1), (16, 1, 192, 96, 1),
+@pytest.mark.parametrize("experts,top,c,f,extra", [(6, 2, 80, 24, 1), (5, 1, 48, 16, 0), (3, 3, 52, 20, 1), (16, 1, 160, 72, 1),
                                                    (64, 6, 1104, 24, 2), (1, 1, 24, 8, 1)])
 def test_sigmoid_routing_weighted_inputs_and_a_shared_expert(experts, top, c, f, extra, dtype):
     from akas_b200.ops import cuda, reference
@@ -746,7 +746,7 @@ def test_a_cached_row_without_a_query_latent(dtype):
 @pytest.mark.gpu
 @pytest.mark.parametrize("activation", ["relu2", "gelu_tanh", "silu"])
 @pytest.mark.parametrize("n,k,o", [(3, 64, 48), (16, 192, 320), (9, 2048, 48), (1, 128, 1008), (40, 264, 528), (128, 2048, 320),
-                                   (300, 192, 256), (700, 512, 1536), (20, 100, 40), (33, 64, 20)])
+                                   (300, 200, 264), (700, 512, 1536), (20, 100, 40), (33, 64, 20)])
 def test_products_with_an_activation_in_the_read_out(n, k, o, activation):
     """The three product kernels' bfloat16 read-out with an activation on the float32 sums, and the fused norm in
     front of it for few tokens, against the product in float32 followed by the activation's own kernel's statement."""
@@ -786,8 +786,8 @@ def test_layer_widths_of_a_real_model(dtype, tmp_path):
 
     retention = dict(heads=8, dim=64, vdim=128, decay=[1.0 - 2.0 ** -(4 + i) for i in range(8)])
     attention = dict(heads=16, kv_heads=4, dim=64, vdim=64, scale=0.125, rot=dict(base=500000.0, dims=64, scaling=dict(factor=8.0)))
-    latent = dict(heads=8, dim=64, rot_dim=32, vdim=64, kv_rank=96, scale=96 ** -0.5,
-                  rot=dict(base=1000000.0, dims=32, scaling=dict(factor=8.0, original=256, fast=32.0, slow=1.0)))
+    latent = dict(heads=8, dim=64, rot_dim=64, vdim=64, kv_rank=64, scale=0.11,
+                  rot=dict(base=1000000.0, dims=64, scaling=dict(factor=4.0, original=256, fast=16.0, slow=2.0)))
     # (only the last layer routes: a choice that falls the other way then moves its own position and no later one)
     config = model(1024, 2048, [ret(retention, dense(4096)), att(attention, dense(1024)), lat(latent, dense(2048)),
                                 ret(retention, moe(512, 16, 3, shared=1024))], loop=(1, 3, 2), eps=1e-6, logit_scale=1024 ** -0.5)
